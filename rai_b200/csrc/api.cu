@@ -1,0 +1,276 @@
+// Context, memory, KV-cache management and the dispatch of the fused entry points to their kernels.
+#include <stdarg.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <string>
+
+#include "ctx.h"
+
+namespace rb {
+
+static thread_local std::string g_last_error;
+
+void set_error(const char* fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+}
+
+int fail(int code, const char* fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+
+}  // namespace rb
+
+using namespace rb;
+
+extern "C" const char* rb_last_error(void) { return g_last_error.c_str(); }
+
+extern "C" int32_t rb_init(int32_t device, rb_ctx** out) {
+  RB_REQUIRE(out, "rb_init: null output");
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0)
+    return fail(RB_ERR_CUDA, "rb_init: no CUDA device available (%s); this library has no CPU path",
+                e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+  RB_REQUIRE(device >= 0 && device < count, "rb_init: device %d out of range (0..%d)", device, count - 1);
+  RB_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  RB_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10)
+    return fail(RB_ERR_UNIMPLEMENTED, "rb_init: device %d is sm_%d%d; this library is built for sm_100a only", device,
+                prop.major, prop.minor);
+  rb_ctx* c = new rb_ctx();
+  c->device = device;
+  c->sm_count = prop.multiProcessorCount;
+  RB_CUDA(cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking));
+  c->stream = c->own_stream;
+  RB_CUDA(cudaMalloc(&c->status_dev, 4 * sizeof(uint32_t)));
+  RB_CUDA(cudaMemset(c->status_dev, 0, 4 * sizeof(uint32_t)));
+  const char* dbg = getenv("RAI_B200_SIMPLE");
+  c->debug_simple = dbg && dbg[0] == '1';
+  *out = c;
+  return RB_OK;
+}
+
+extern "C" int32_t rb_destroy(rb_ctx* ctx) {
+  if (!ctx) return RB_OK;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  if (ctx->status_dev) cudaFree(ctx->status_dev);
+  if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
+  delete ctx;
+  return RB_OK;
+}
+
+extern "C" int32_t rb_set_stream(rb_ctx* ctx, void* s) {
+  RB_REQUIRE(ctx, "rb_set_stream: null context");
+  ctx->stream = s ? (cudaStream_t)s : ctx->own_stream;
+  return RB_OK;
+}
+
+extern "C" int32_t rb_status_word(rb_ctx* ctx, uint32_t* out4) {
+  RB_REQUIRE(ctx && out4, "rb_status_word: null argument");
+  RB_CUDA(cudaStreamSynchronize(ctx->stream));
+  RB_CUDA(cudaMemcpy(out4, ctx->status_dev, 4 * sizeof(uint32_t), cudaMemcpyDeviceToHost));
+  return RB_OK;
+}
+
+extern "C" int32_t rb_sync(rb_ctx* ctx) {
+  RB_REQUIRE(ctx, "rb_sync: null context");
+  uint32_t w[4];
+  RB_TRY(rb_status_word(ctx, w));
+  if (w[0] != 0) {
+    RB_CUDA(cudaMemset(ctx->status_dev, 0, 4 * sizeof(uint32_t)));
+    const int code = -(int)w[0];
+    return fail(code, "device-side check failed: code %d at 0x%x (detail %u, %u)", code, w[1], w[2], w[3]);
+  }
+  return RB_OK;
+}
+
+extern "C" int32_t rb_sm_count(rb_ctx* ctx) { return ctx ? ctx->sm_count : 0; }
+extern "C" int64_t rb_launch_count(rb_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+extern "C" int32_t rb_malloc(rb_ctx* ctx, size_t bytes, void** out) {
+  RB_REQUIRE(ctx && out, "rb_malloc: null argument");
+  *out = nullptr;
+  if (bytes == 0) return RB_OK;
+  cudaError_t e = cudaMalloc(out, bytes);
+  if (e == cudaErrorMemoryAllocation) {
+    cudaGetLastError();
+    return fail(RB_ERR_OOM, "rb_malloc: out of device memory asking for %zu bytes", bytes);
+  }
+  RB_CUDA(e);
+  return RB_OK;
+}
+
+extern "C" int32_t rb_free(rb_ctx* ctx, void* dev) {
+  RB_REQUIRE(ctx, "rb_free: null context");
+  if (!dev) return RB_OK;
+  RB_CUDA(cudaStreamSynchronize(ctx->stream));
+  // tensor maps built over this allocation must not outlive it
+  for (auto it = ctx->tmaps.begin(); it != ctx->tmaps.end();)
+    it = (std::get<0>(it->first) == dev) ? ctx->tmaps.erase(it) : std::next(it);
+  RB_CUDA(cudaFree(dev));
+  return RB_OK;
+}
+
+extern "C" int32_t rb_upload(rb_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  RB_REQUIRE(ctx && (bytes == 0 || (dst && src)), "rb_upload: null argument");
+  if (bytes) RB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+  return RB_OK;
+}
+
+extern "C" int32_t rb_download(rb_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  RB_REQUIRE(ctx && (bytes == 0 || (dst && src)), "rb_download: null argument");
+  if (bytes) RB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  RB_CUDA(cudaStreamSynchronize(ctx->stream));
+  return RB_OK;
+}
+
+// ------------------------------------------------------------------------------------------ KV cache
+extern "C" int32_t rb_kv_cache_create(rb_ctx* ctx, int32_t layers, int32_t kv_heads, int32_t head_dim,
+                                      int32_t max_batch, int32_t max_seq, int32_t dtype, rb_kv_cache** out) {
+  RB_REQUIRE(ctx && out, "rb_kv_cache_create: null argument");
+  RB_REQUIRE(layers > 0 && kv_heads > 0 && head_dim > 0 && max_batch > 0 && max_seq > 0, "rb_kv_cache_create: bad sizes");
+  RB_REQUIRE(dtype == RB_BF16 || dtype == RB_F32, "rb_kv_cache_create: dtype %d unsupported", dtype);
+  RB_REQUIRE(head_dim % 8 == 0 && head_dim <= 256, "rb_kv_cache_create: head_dim %d unsupported", head_dim);
+  rb_kv_cache* c = new rb_kv_cache();
+  c->ctx = ctx;
+  c->layers = layers; c->kv_heads = kv_heads; c->head_dim = head_dim;
+  c->max_batch = max_batch; c->dtype = dtype;
+  c->pages_per_seq = (max_seq + kPageTokens - 1) / kPageTokens;
+  c->max_seq = c->pages_per_seq * kPageTokens;
+  c->num_pages = c->pages_per_seq * max_batch;
+  const size_t bytes = (size_t)layers * c->layer_stride_elems() * dtype_size(dtype);
+  int st = rb_malloc(ctx, bytes, &c->k);
+  if (st == RB_OK) st = rb_malloc(ctx, bytes, &c->v);
+  if (st == RB_OK) st = rb_malloc(ctx, (size_t)c->num_pages * sizeof(int32_t), (void**)&c->block_table);
+  if (st == RB_OK) st = rb_malloc(ctx, (size_t)max_batch * sizeof(int32_t), (void**)&c->seq_lens);
+  if (st != RB_OK) { rb_kv_cache_destroy(c); return st; }
+  // Zero the pages: the tail of a sequence's last page is read (and masked) by the attention
+  // kernels, so it must hold finite values.
+  RB_CUDA(cudaMemsetAsync(c->k, 0, bytes, ctx->stream));
+  RB_CUDA(cudaMemsetAsync(c->v, 0, bytes, ctx->stream));
+  std::vector<int32_t> bt(c->num_pages);
+  for (int i = 0; i < c->num_pages; ++i) bt[i] = i;  // sequence b owns pages [b*pages_per_seq, ...)
+  RB_CUDA(cudaMemcpyAsync(c->block_table, bt.data(), bt.size() * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+  RB_CUDA(cudaMemsetAsync(c->seq_lens, 0, (size_t)max_batch * sizeof(int32_t), ctx->stream));
+  RB_CUDA(cudaStreamSynchronize(ctx->stream));
+  c->host_lens.assign(max_batch, 0);
+  *out = c;
+  return RB_OK;
+}
+
+extern "C" int32_t rb_kv_cache_destroy(rb_kv_cache* c) {
+  if (!c) return RB_OK;
+  cudaStreamSynchronize(c->ctx->stream);
+  if (c->k) cudaFree(c->k);
+  if (c->v) cudaFree(c->v);
+  if (c->block_table) cudaFree(c->block_table);
+  if (c->seq_lens) cudaFree(c->seq_lens);
+  delete c;
+  return RB_OK;
+}
+
+extern "C" int32_t rb_kv_cache_reset(rb_kv_cache* c) {
+  RB_REQUIRE(c, "rb_kv_cache_reset: null cache");
+  RB_CUDA(cudaMemsetAsync(c->seq_lens, 0, (size_t)c->max_batch * sizeof(int32_t), c->ctx->stream));
+  c->host_lens.assign(c->max_batch, 0);
+  return RB_OK;
+}
+
+extern "C" int32_t rb_kv_cache_set_len(rb_kv_cache* c, int32_t batch, int32_t len) {
+  RB_REQUIRE(c, "rb_kv_cache_set_len: null cache");
+  RB_REQUIRE(batch > 0 && batch <= c->max_batch, "rb_kv_cache_set_len: batch %d exceeds capacity %d", batch, c->max_batch);
+  RB_REQUIRE(len >= 0 && len <= c->max_seq, "rb_kv_cache_set_len: length %d exceeds capacity %d", len, c->max_seq);
+  for (int b = 0; b < batch; ++b) c->host_lens[b] = len;
+  // host_lens is a std::vector that outlives the copy; pageable source: the copy is staged by the runtime
+  RB_CUDA(cudaMemcpyAsync(c->seq_lens, c->host_lens.data(), (size_t)batch * sizeof(int32_t), cudaMemcpyHostToDevice,
+                          c->ctx->stream));
+  return RB_OK;
+}
+
+extern "C" int32_t rb_kv_cache_read(rb_kv_cache* c, int32_t layer, int32_t seq, int32_t kv_head, int32_t t0, int32_t n,
+                                    void* k_host, void* v_host) {
+  RB_REQUIRE(c && k_host && v_host, "rb_kv_cache_read: null argument");
+  RB_REQUIRE(layer >= 0 && layer < c->layers && seq >= 0 && seq < c->max_batch && kv_head >= 0 && kv_head < c->kv_heads,
+             "rb_kv_cache_read: index out of range");
+  RB_REQUIRE(t0 >= 0 && n >= 0 && t0 + n <= c->max_seq, "rb_kv_cache_read: token range out of capacity");
+  const size_t es = dtype_size(c->dtype), row = (size_t)c->head_dim * es;
+  RB_CUDA(cudaStreamSynchronize(c->ctx->stream));
+  for (int i = 0; i < n; ++i) {
+    const int t = t0 + i;
+    const int page = seq * c->pages_per_seq + t / kPageTokens;  // identity block table
+    const size_t off = ((size_t)layer * c->layer_stride_elems() +
+                        (((size_t)page * c->kv_heads + kv_head) * kPageTokens + t % kPageTokens) * c->head_dim) * es;
+    RB_CUDA(cudaMemcpy((char*)k_host + i * row, (char*)c->k + off, row, cudaMemcpyDeviceToHost));
+    RB_CUDA(cudaMemcpy((char*)v_host + i * row, (char*)c->v + off, row, cudaMemcpyDeviceToHost));
+  }
+  return RB_OK;
+}
+
+// ------------------------------------------------------------------------------------------ fused ops
+extern "C" int32_t rb_linear(rb_ctx* ctx, const void* x, const void* w, const void* bias, const void* residual,
+                             void* out, int64_t m, int64_t n, int64_t k, int32_t act, int32_t dtype) {
+  RB_REQUIRE(ctx && x && w && out, "rb_linear: null argument");
+  RB_REQUIRE(m >= 0 && n > 0 && k > 0, "rb_linear: bad sizes");
+  GemmArgs a;
+  a.x = x; a.w = w; a.bias = bias; a.residual = residual; a.out = out;
+  a.m = m; a.n = n; a.k = k; a.act = act;
+  if (dtype == RB_BF16 && !ctx->debug_simple) return gemm_tc_bf16(ctx, a);
+  return gemm_simple(ctx, a, dtype);
+}
+
+extern "C" int32_t rb_gated_linear(rb_ctx* ctx, const void* x, const void* wg, const void* wu, void* out, int64_t m,
+                                   int64_t n, int64_t k, int32_t act, int32_t dtype) {
+  RB_REQUIRE(ctx && x && wg && wu && out, "rb_gated_linear: null argument");
+  RB_REQUIRE(m >= 0 && n > 0 && k > 0, "rb_gated_linear: bad sizes");
+  GemmArgs a;
+  a.x = x; a.w = wg; a.w2 = wu; a.out = out;
+  a.m = m; a.n = n; a.k = k; a.act = act;
+  if (dtype == RB_BF16 && !ctx->debug_simple) return gemm_tc_bf16(ctx, a);
+  return gemm_simple(ctx, a, dtype);
+}
+
+extern "C" int32_t rb_linear_partials(rb_ctx* ctx, const void* x, const void* w, float* part, int64_t m, int64_t n,
+                                      int64_t k, int32_t n_split) {
+  RB_REQUIRE(ctx && x && w && part, "rb_linear_partials: null argument");
+  RB_REQUIRE(m > 0 && m <= 256 && n > 0 && k > 0 && n_split >= 1, "rb_linear_partials: bad sizes (M must be <= 256)");
+  GemmArgs a;
+  a.x = x; a.w = w; a.out = part;
+  a.m = m; a.n = n; a.k = k;
+  a.n_split = n_split; a.partials = true;
+  if (!ctx->debug_simple) return gemm_tc_bf16(ctx, a);
+  return gemm_simple(ctx, a, RB_BF16);
+}
+
+extern "C" int32_t rb_linear_pick_splits(rb_ctx* ctx, int64_t m, int64_t n, int64_t k) {
+  if (!ctx || m <= 0 || n <= 0 || k <= 0) return 1;
+  return gemm_tc_pick_splits(ctx, m, n, k);
+}
+
+extern "C" int32_t rb_attention(rb_ctx* ctx, const void* q, rb_kv_cache* c, int32_t layer, int32_t batch, int32_t s_new,
+                                int32_t q_heads, float scale, void* out, int32_t dtype) {
+  RB_REQUIRE(ctx && q && c && out, "rb_attention: null argument");
+  RB_REQUIRE(dtype == c->dtype, "rb_attention: cache dtype differs");
+  RB_REQUIRE(layer >= 0 && layer < c->layers, "rb_attention: layer %d out of range", layer);
+  RB_REQUIRE(batch > 0 && batch <= c->max_batch && s_new > 0, "rb_attention: bad batch/seq");
+  RB_REQUIRE(q_heads > 0 && q_heads % c->kv_heads == 0, "rb_attention: %d query heads over %d KV heads", q_heads,
+             c->kv_heads);
+  for (int b = 0; b < batch; ++b)
+    RB_REQUIRE(c->host_lens[b] >= s_new, "rb_attention: sequence %d holds %d tokens, fewer than the %d new ones", b,
+               c->host_lens[b], s_new);
+  if (dtype == RB_BF16 && !ctx->debug_simple) return attention_mma_bf16(ctx, q, c, layer, batch, s_new, q_heads, scale, out);
+  return attention_simple(ctx, q, c, layer, batch, s_new, q_heads, scale, out, dtype);
+}

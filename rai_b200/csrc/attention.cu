@@ -1,0 +1,427 @@
+// Attention over the paged bf16 KV cache, replacing repeat_kv + QK^T*scale + mask + softmax + PV
+// (rai-models/src/llm/qwen2.rs:205-216, phi2.rs:245-261, phi3.rs:199-209, gemma.rs:238-249).
+// Scores, masks and repeated KV heads are never materialised: a 64-key tile of K and V is staged
+// in shared memory with 16-byte cp.async copies (a cache page IS one tile, so every copy is a
+// contiguous 64 x head_dim block), scores live in registers as mma.sync fragments, and the softmax
+// is the online (running max / running sum) form in float32.
+//
+//   prefill  grid (q tiles of 64 rows, q heads, batch): each of the 4 warps owns 16 query rows and
+//            walks the causal range of key tiles.
+//   decode   grid (KV splits, kv heads, batch): the G = q_heads / kv_heads query heads that share
+//            a KV head are packed as the 16 rows of one MMA tile, so K and V are read from HBM once
+//            per KV head instead of G times; the 4 warps split each key tile 16 keys apiece and
+//            merge their (max, sum, O) at the end.  With more than one split a small kernel merges
+//            the per-split partials.
+// HBM-bound at decode: algorithmic bytes = 2 * len * kv_heads * head_dim * 2 per sequence and layer.
+#include <algorithm>
+
+#include "ctx.h"
+
+namespace rb {
+
+using bf16 = __nv_bfloat16;
+
+namespace {
+
+constexpr int kTile = 64;  // keys per tile == tokens per cache page
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int D, bool DECODE>
+struct ACfg {
+  static constexpr int kDP = D + 8;                      // padded row: conflict-free ldmatrix
+  static constexpr int kRowBytes = kDP * 2;
+  static constexpr int kStages = (DECODE && D <= 128) ? 3 : 2;
+  static constexpr int kQRows = DECODE ? 16 : 64;
+  static constexpr int kTileBytes = kTile * kRowBytes;   // one of K or V
+  static constexpr int kStageBytes = 2 * kTileBytes;
+  static constexpr int kQBytes = kQRows * kRowBytes;
+  static constexpr int kMergeBytes = DECODE ? (4 * 16 * D + 2 * 4 * 16) * 4 : 0;
+  static constexpr int kPipeBytes = kStages * kStageBytes + kQBytes;
+  static constexpr int kSmemBytes = kPipeBytes > kMergeBytes ? kPipeBytes : kMergeBytes;
+  static constexpr bool kQInRegs = D <= 128;
+  static constexpr int kKeysPerWarp = DECODE ? 16 : 64;
+  static constexpr int kNtS = kKeysPerWarp / 8;
+};
+
+struct AParams {
+  const bf16* q;
+  const bf16* k;  // layer base
+  const bf16* v;
+  const int32_t* block_table;
+  const int32_t* seq_lens;
+  int pages_per_seq, s_new, q_heads, kv_heads, group;
+  int n_splits;
+  float scale_log2;
+  bf16* out;
+  float* part_o;   // [batch*q_heads][n_splits][D]
+  float* part_ml;  // [batch*q_heads][n_splits][2]
+};
+
+template <int D, bool DECODE>
+__global__ void __launch_bounds__(128, (D <= 128) ? 2 : 1) attention_kernel(const AParams p) {
+  using C = ACfg<D, DECODE>;
+  extern __shared__ __align__(16) uint8_t smem[];
+  uint8_t* q_s = smem;
+  uint8_t* kv_s = smem + C::kQBytes;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+
+  int b, head, kvh, q0 = 0, split = 0;
+  if (DECODE) {
+    split = blockIdx.x; kvh = blockIdx.y; b = blockIdx.z; head = kvh * p.group;
+  } else {
+    q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * 64;  // longest causal ranges first
+    head = blockIdx.y; b = blockIdx.z; kvh = head / p.group;
+  }
+  const int len = p.seq_lens[b];
+  const int base = len - p.s_new;  // absolute position of query row 0
+
+  // key tiles this CTA walks
+  int tile_lo, tile_hi;
+  if (DECODE) {
+    const int total = (len + kTile - 1) / kTile;
+    const int per = (total + p.n_splits - 1) / p.n_splits;
+    tile_lo = split * per;
+    tile_hi = min(total, tile_lo + per);
+  } else {
+    tile_lo = 0;
+    tile_hi = (min(base + q0 + 64, len) + kTile - 1) / kTile;
+  }
+
+  // ---- stage Q (rows beyond the valid range are zero)
+  {
+    constexpr int chunks_per_row = D / 8;
+    for (int i = threadIdx.x; i < C::kQRows * chunks_per_row; i += blockDim.x) {
+      const int r = i / chunks_per_row, c = i % chunks_per_row;
+      const bf16* src = nullptr;
+      if (DECODE) {
+        if (r < p.group) src = p.q + ((size_t)b * p.q_heads + head + r) * D + c * 8;
+      } else {
+        if (q0 + r < p.s_new) src = p.q + (((size_t)b * p.s_new + q0 + r) * p.q_heads + head) * D + c * 8;
+      }
+      const uint32_t dst = s_u32(q_s + r * C::kRowBytes + c * 16);
+      if (src) cp_async16(dst, src);
+      else *reinterpret_cast<uint4*>(q_s + r * C::kRowBytes + c * 16) = make_uint4(0, 0, 0, 0);
+    }
+  }
+  auto load_tile = [&](int tile, int stage) {
+    const int page = p.block_table[(size_t)b * p.pages_per_seq + tile];
+    const size_t off = ((size_t)page * p.kv_heads + kvh) * kTile * D;
+    const bf16* ksrc = p.k + off;
+    const bf16* vsrc = p.v + off;
+    uint8_t* ks = kv_s + stage * C::kStageBytes;
+    uint8_t* vs = ks + C::kTileBytes;
+    constexpr int chunks_per_row = D / 8;
+    for (int i = threadIdx.x; i < kTile * chunks_per_row; i += blockDim.x) {
+      const int r = i / chunks_per_row, c = i % chunks_per_row;
+      cp_async16(s_u32(ks + r * C::kRowBytes + c * 16), ksrc + (size_t)r * D + c * 8);
+      cp_async16(s_u32(vs + r * C::kRowBytes + c * 16), vsrc + (size_t)r * D + c * 8);
+    }
+  };
+  // prologue: Q + the first kStages-1 tiles, one commit group each
+#pragma unroll
+  for (int s = 0; s < C::kStages - 1; ++s) {
+    if (tile_lo + s < tile_hi) load_tile(tile_lo + s, s);
+    cp_async_commit();
+  }
+
+  const int qrow0 = DECODE ? 0 : warp * 16;  // first Q row (inside the CTA tile) of this warp
+  const int kw0 = DECODE ? warp * 16 : 0;    // first key (inside the tile) of this warp
+  uint32_t qf[C::kQInRegs ? D / 16 : 1][4];
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  // causal limit per row half (g, g+8): last visible key index
+  int lim[2];
+  if (DECODE) { lim[0] = lim[1] = len - 1; }
+  else { lim[0] = base + q0 + qrow0 + g; lim[1] = lim[0] + 8; }
+
+  bool q_loaded = false;
+  for (int tile = tile_lo; tile < tile_hi; ++tile) {
+    const int it = tile - tile_lo;
+    {  // keep kStages-1 tiles in flight
+      const int nxt = tile + C::kStages - 1;
+      if (nxt < tile_hi) load_tile(nxt, (it + C::kStages - 1) % C::kStages);
+      cp_async_commit();
+    }
+    cp_async_wait<C::kStages - 1>();
+    __syncthreads();
+    if (C::kQInRegs && !q_loaded) {
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk)
+        ldsm_x4(qf[kk], s_u32(q_s + (qrow0 + (lane & 15)) * C::kRowBytes + (kk * 16 + (lane >> 4) * 8) * 2));
+      q_loaded = true;
+    }
+    const uint8_t* ks = kv_s + (it % C::kStages) * C::kStageBytes;
+    const uint8_t* vs = ks + C::kTileBytes;
+    const int tile_start = tile * kTile;
+    // a warp whose rows all precede this tile has nothing to do (prefill, diagonal tiles only)
+    // (warp-uniform by construction: mma.sync and ldmatrix need every lane)
+    const bool warp_active = DECODE ? (tile_start + kw0 < len) : (tile_start <= base + q0 + qrow0 + 15);
+    if (warp_active) {
+      float s[C::kNtS][4];
+#pragma unroll
+      for (int i = 0; i < C::kNtS; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t a[4];
+        if (C::kQInRegs) { a[0] = qf[kk][0]; a[1] = qf[kk][1]; a[2] = qf[kk][2]; a[3] = qf[kk][3]; }
+        else ldsm_x4(a, s_u32(q_s + (qrow0 + (lane & 15)) * C::kRowBytes + (kk * 16 + (lane >> 4) * 8) * 2));
+#pragma unroll
+        for (int np = 0; np < C::kNtS / 2; ++np) {
+          uint32_t bb[4];
+          const int key = kw0 + np * 16 + (lane & 7) + ((lane >> 4) << 3);
+          const int dc = kk * 16 + (((lane >> 3) & 1) << 3);
+          ldsm_x4(bb, s_u32(ks + key * C::kRowBytes + dc * 2));
+          mma16816(s[2 * np], a, bb[0], bb[1]);
+          mma16816(s[2 * np + 1], a, bb[2], bb[3]);
+        }
+      }
+      // scale, mask, online softmax
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < C::kNtS; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key_abs = tile_start + kw0 + nt * 8 + 2 * t + (e & 1);
+          const int hf = e >> 1;
+          const float v = (key_abs <= lim[hf]) ? s[nt][e] * p.scale_log2 : -INFINITY;
+          s[nt][e] = v;
+          mx[hf] = fmaxf(mx[hf], v);
+        }
+      float corr[2], m_use[2];
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 1));
+        mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 2));
+        const float m_new = fmaxf(m_run[hf], mx[hf]);
+        m_use[hf] = (m_new == -INFINITY) ? 0.f : m_new;
+        corr[hf] = exp2f(m_run[hf] - m_use[hf]);
+        m_run[hf] = m_new;
+        l_run[hf] *= corr[hf];
+      }
+      uint32_t pa[C::kKeysPerWarp / 16][4];
+#pragma unroll
+      for (int nt = 0; nt < C::kNtS; ++nt) {
+        const float p0 = exp2f(s[nt][0] - m_use[0]), p1 = exp2f(s[nt][1] - m_use[0]);
+        const float p2 = exp2f(s[nt][2] - m_use[1]), p3 = exp2f(s[nt][3] - m_use[1]);
+        l_run[0] += p0 + p1;
+        l_run[1] += p2 + p3;
+        pa[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16(p0, p1);
+        pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
+      }
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
+      // O += P V
+#pragma unroll
+      for (int k2 = 0; k2 < C::kKeysPerWarp / 16; ++k2)
+#pragma unroll
+        for (int dp = 0; dp < D / 16; ++dp) {
+          uint32_t bb[4];
+          const int key = kw0 + k2 * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+          const int dc = dp * 16 + ((lane >> 4) << 3);
+          ldsm_x4_t(bb, s_u32(vs + key * C::kRowBytes + dc * 2));
+          mma16816(o[2 * dp], pa[k2], bb[0], bb[1]);
+          mma16816(o[2 * dp + 1], pa[k2], bb[2], bb[3]);
+        }
+    }
+    __syncthreads();  // the stage is overwritten by the next iteration's prefetch
+  }
+  cp_async_wait<0>();
+
+  // row sums across the quad
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    l_run[hf] += __shfl_xor_sync(0xffffffffu, l_run[hf], 1);
+    l_run[hf] += __shfl_xor_sync(0xffffffffu, l_run[hf], 2);
+  }
+
+  if (!DECODE) {
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int row = q0 + qrow0 + g + hf * 8;
+      if (row >= p.s_new) continue;
+      const float inv = 1.0f / l_run[hf];
+      bf16* dst = p.out + (((size_t)b * p.s_new + row) * p.q_heads + head) * D;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i)
+        *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t) = pack_bf16(o[i][hf * 2] * inv, o[i][hf * 2 + 1] * inv);
+    }
+    return;
+  }
+
+  // ---- decode: merge the 4 warps' partial states through shared memory
+  __syncthreads();
+  float* mo = reinterpret_cast<float*>(smem);          // [4][16][D]
+  float* mm = mo + 4 * 16 * D;                         // [4][16]
+  float* ml = mm + 4 * 16;                             // [4][16]
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    const int row = g + hf * 8;
+    if (t == 0) { mm[warp * 16 + row] = m_run[hf]; ml[warp * 16 + row] = l_run[hf]; }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      mo[(warp * 16 + row) * D + i * 8 + 2 * t] = o[i][hf * 2];
+      mo[(warp * 16 + row) * D + i * 8 + 2 * t + 1] = o[i][hf * 2 + 1];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < p.group * D; idx += blockDim.x) {
+    const int row = idx / D, dd = idx % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, mm[w * 16 + row]);
+    const float Mu = (M == -INFINITY) ? 0.f : M;
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float sc = exp2f(mm[w * 16 + row] - Mu);
+      L += ml[w * 16 + row] * sc;
+      O += mo[(w * 16 + row) * D + dd] * sc;
+    }
+    const size_t bh = (size_t)b * p.q_heads + head + row;
+    if (p.n_splits == 1) {
+      p.out[bh * D + dd] = __float2bfloat16_rn(O / L);
+    } else {
+      p.part_o[(bh * p.n_splits + split) * D + dd] = O;
+      if (dd == 0) { p.part_ml[(bh * p.n_splits + split) * 2] = M; p.part_ml[(bh * p.n_splits + split) * 2 + 1] = L; }
+    }
+  }
+}
+
+// Merges the per-split (max, sum, O) of the decode kernel: one block per (sequence, head).
+__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                       int n_splits, int d, bf16* __restrict__ out) {
+  const size_t bh = blockIdx.x;
+  float M = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(bh * n_splits + s) * 2]);
+  const float Mu = (M == -INFINITY) ? 0.f : M;
+  float L = 0.f;
+  for (int s = 0; s < n_splits; ++s) L += part_ml[(bh * n_splits + s) * 2 + 1] * exp2f(part_ml[(bh * n_splits + s) * 2] - Mu);
+  for (int dd = threadIdx.x; dd < d; dd += blockDim.x) {
+    float O = 0.f;
+    for (int s = 0; s < n_splits; ++s)
+      O += part_o[(bh * n_splits + s) * d + dd] * exp2f(part_ml[(bh * n_splits + s) * 2] - Mu);
+    out[bh * d + dd] = __float2bfloat16_rn(O / L);
+  }
+}
+
+struct Scratch {
+  float* ptr = nullptr;
+  size_t bytes = 0;
+};
+std::map<int, Scratch>& scratch_by_device() {
+  static std::map<int, Scratch> m;
+  return m;
+}
+
+template <int D>
+int launch_attention(rb_ctx* ctx, AParams& p, int batch, int max_len) {
+  if (p.s_new > 1) {
+    using C = ACfg<D, false>;
+    auto kern = attention_kernel<D, false>;
+    static bool set = false;
+    if (!set) { RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes)); set = true; }
+    dim3 grid((unsigned)((p.s_new + 63) / 64), (unsigned)p.q_heads, (unsigned)batch);
+    p.n_splits = 1;
+    kern<<<grid, 128, C::kSmemBytes, ctx->stream>>>(p);
+    ctx->launches++;
+    return launch_status("attention_prefill");
+  }
+  using C = ACfg<D, true>;
+  auto kern = attention_kernel<D, true>;
+  static bool set = false;
+  if (!set) { RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes)); set = true; }
+  const int tiles = std::max(1, (max_len + kTile - 1) / kTile);
+  const int work = batch * p.kv_heads;
+  int splits = (2 * ctx->sm_count + work - 1) / work;
+  splits = std::max(1, std::min(splits, std::min(tiles, 32)));
+  if (splits > 1) {  // no split may be shorter than 2 tiles: the merge costs more than it saves
+    splits = std::max(1, std::min(splits, tiles / 2));
+  }
+  p.n_splits = splits;
+  if (splits > 1) {
+    const size_t need = (size_t)batch * p.q_heads * splits * (D + 2) * sizeof(float);
+    Scratch& sc = scratch_by_device()[ctx->device];
+    if (sc.bytes < need) {
+      if (sc.ptr) RB_CUDA(cudaFree(sc.ptr));
+      sc.ptr = nullptr; sc.bytes = 0;
+      RB_CUDA(cudaMalloc(&sc.ptr, need));
+      sc.bytes = need;
+    }
+    p.part_o = sc.ptr;
+    p.part_ml = sc.ptr + (size_t)batch * p.q_heads * splits * D;
+  }
+  dim3 grid((unsigned)splits, (unsigned)p.kv_heads, (unsigned)batch);
+  kern<<<grid, 128, C::kSmemBytes, ctx->stream>>>(p);
+  ctx->launches++;
+  RB_TRY(launch_status("attention_decode"));
+  if (splits > 1) {
+    attention_merge_kernel<<<batch * p.q_heads, 128, 0, ctx->stream>>>(p.part_o, p.part_ml, splits, D, p.out);
+    ctx->launches++;
+    RB_TRY(launch_status("attention_merge"));
+  }
+  return RB_OK;
+}
+
+}  // namespace
+
+int attention_mma_bf16(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, int batch, int s_new, int q_heads,
+                       float scale, void* out) {
+  AParams p{};
+  const size_t loff = (size_t)layer * c->layer_stride_elems();
+  p.q = (const bf16*)q;
+  p.k = (const bf16*)c->k + loff;
+  p.v = (const bf16*)c->v + loff;
+  p.block_table = c->block_table;
+  p.seq_lens = c->seq_lens;
+  p.pages_per_seq = c->pages_per_seq;
+  p.s_new = s_new;
+  p.q_heads = q_heads;
+  p.kv_heads = c->kv_heads;
+  p.group = q_heads / c->kv_heads;
+  p.scale_log2 = scale * kLog2e;
+  p.out = (bf16*)out;
+  RB_REQUIRE(p.group >= 1 && p.group <= 16 && q_heads % c->kv_heads == 0,
+             "attention: %d query heads per KV head unsupported (1..16)", p.group);
+  int max_len = 0;
+  for (int b = 0; b < batch; ++b) max_len = std::max(max_len, c->host_lens[b]);
+  switch (c->head_dim) {
+    case 64: return launch_attention<64>(ctx, p, batch, max_len);
+    case 80: return launch_attention<80>(ctx, p, batch, max_len);
+    case 96: return launch_attention<96>(ctx, p, batch, max_len);
+    case 128: return launch_attention<128>(ctx, p, batch, max_len);
+    case 256: return launch_attention<256>(ctx, p, batch, max_len);
+  }
+  return fail(RB_ERR_UNIMPLEMENTED, "attention: head_dim %d has no tensor-core kernel (64, 80, 96, 128, 256)",
+              c->head_dim);
+}
+
+}  // namespace rb

@@ -1,0 +1,105 @@
+// Shared declarations of the rai_b200 library: status codes, dtype tags, error reporting,
+// small device helpers.  Everything here is internal; the exported surface is include/rai_b200.h.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string>
+
+#include "../../include/rai_b200.h"
+
+namespace rb {
+
+// Last error text of the calling thread (read through rb_last_error()).
+void set_error(const char* fmt, ...);
+int fail(int code, const char* fmt, ...);
+
+#define RB_CUDA(expr)                                                                         \
+  do {                                                                                        \
+    cudaError_t _e = (expr);                                                                  \
+    if (_e != cudaSuccess)                                                                    \
+      return ::rb::fail(RB_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e),  \
+                        __FILE__, __LINE__);                                                  \
+  } while (0)
+
+#define RB_TRY(expr)                \
+  do {                              \
+    int _s = (expr);                \
+    if (_s != RB_OK) return _s;     \
+  } while (0)
+
+#define RB_REQUIRE(cond, ...)                                        \
+  do {                                                               \
+    if (!(cond)) return ::rb::fail(RB_ERR_INVALID, __VA_ARGS__);     \
+  } while (0)
+
+inline int launch_status(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(RB_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
+  return RB_OK;
+}
+
+inline size_t dtype_size(int dt) {
+  switch (dt) {
+    case RB_U8: return 1;
+    case RB_F16: case RB_BF16: return 2;
+    case RB_U32: case RB_F32: return 4;
+    case RB_I64: case RB_F64: return 8;
+  }
+  return 0;
+}
+
+// Device status word: kernels that wait on barriers record a give-up here instead of trapping.
+// Layout: [0] = error code (0 ok), [1] = where (kernel-specific tag), [2..3] = details.
+uint32_t* device_status_word();  // device pointer (per current device), zero-initialised
+
+template <typename T> struct Cvt;
+template <> struct Cvt<float> {
+  __device__ __forceinline__ static float to_f(float v) { return v; }
+  __device__ __forceinline__ static float from_f(float v) { return v; }
+};
+template <> struct Cvt<__nv_bfloat16> {
+  __device__ __forceinline__ static float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  __device__ __forceinline__ static __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum for blocks of up to 1024 threads; `red` is 32 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+// Activation tags shared by the GEMM epilogues and the elementwise kernels
+// (rai-core/src/hlops/activations.rs:20-32).
+__device__ __forceinline__ float act_apply(int act, float x) {
+  switch (act) {
+    case RB_ACT_SILU: return x / (__expf(-x) + 1.0f);
+    case RB_ACT_GELU_TANH: {
+      const float c = 0.7978845608028654f;
+      return 0.5f * x * (1.0f + tanhf(c * (x + 0.044715f * x * x * x)));
+    }
+    case RB_ACT_GELU_ERF: return x * 0.5f * (1.0f + erff(x * 0.7071067811865476f));
+    case RB_ACT_RELU: return fmaxf(x, 0.f);
+    default: return x;
+  }
+}
+
+}  // namespace rb

@@ -1,0 +1,64 @@
+// Internal definition of the context and the KV cache behind the opaque handles of the C ABI.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <map>
+#include <tuple>
+#include <vector>
+
+#include "common.cuh"
+
+struct rb_ctx {
+  int device = 0;
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t stream = nullptr;
+  int sm_count = 148;
+  uint32_t* status_dev = nullptr;  // 4 words, see rb_status_word
+  int64_t launches = 0;
+  // Tensor maps are keyed by (base pointer, rows, cols, row stride in elements, box rows).
+  std::map<std::tuple<const void*, int64_t, int64_t, int64_t, int>, CUtensorMap> tmaps;
+  bool debug_simple = false;  // RAI_B200_SIMPLE=1: route bf16 through the plain kernels (debugging aid)
+};
+
+// Pages of 64 tokens.  K and V each: [layer][page][kv_head][64][head_dim] in the cache dtype.
+struct rb_kv_cache {
+  rb_ctx* ctx = nullptr;
+  int layers = 0, kv_heads = 0, head_dim = 0, max_batch = 0, max_seq = 0, dtype = RB_BF16;
+  int pages_per_seq = 0, num_pages = 0;
+  void* k = nullptr;
+  void* v = nullptr;
+  int32_t* block_table = nullptr;  // device [max_batch][pages_per_seq]
+  int32_t* seq_lens = nullptr;     // device [max_batch]
+  std::vector<int32_t> host_lens;
+  size_t layer_stride_elems() const { return (size_t)num_pages * kv_heads * 64 * head_dim; }
+};
+
+namespace rb {
+constexpr int kPageTokens = 64;
+
+// Internal launchers shared between api.cu and model.cu (defined next to their kernels).
+int tmap_2d_bf16(rb_ctx* ctx, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows,
+                 const CUtensorMap** out);
+
+struct GemmArgs {
+  const void* x = nullptr;      // [M, K]
+  const void* w = nullptr;      // [N, K]
+  const void* w2 = nullptr;     // gated: up weights [N, K]
+  const void* bias = nullptr;   // [N]
+  const void* residual = nullptr;  // [M, N]
+  void* out = nullptr;          // [M, N] (model dtype) or float partials [n_split][M][N]
+  int64_t m = 0, n = 0, k = 0;
+  int act = RB_ACT_NONE;
+  int n_split = 1;              // > 1: write float partials, no epilogue
+  bool partials = false;
+};
+int gemm_tc_bf16(rb_ctx* ctx, const GemmArgs& a);
+int gemm_tc_pick_splits(rb_ctx* ctx, int64_t m, int64_t n, int64_t k);
+int gemm_simple(rb_ctx* ctx, const GemmArgs& a, int dtype);
+
+int attention_mma_bf16(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, int batch, int s_new, int q_heads,
+                       float scale, void* out);
+int attention_simple(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, int batch, int s_new, int q_heads,
+                     float scale, void* out, int dtype);
+}  // namespace rb

@@ -1,0 +1,614 @@
+// Decoder driver: the host side of Model::new / update_by_safetensors / Model::fwd / clear_kv_cache of
+// rai-models/src/llm/{qwen2,phi2,phi3,gemma}.rs, issuing the fused kernel sequence per layer:
+//
+//   norm(+pending residual sum)  ->  qkv GEMM  ->  RoPE + head split + KV append  ->  attention
+//   ->  o_proj GEMM (+residual)  ->  norm  ->  gate/up GEMM (+act*mul)  ->  down GEMM (+residual)
+//
+// Residual adds never run as kernels of their own: a GEMM either adds the residual stream in its
+// epilogue (large M) or leaves float32 split-K partials / a tensor-parallel partial sum "pending",
+// and the next norm kernel folds the pending terms into the residual stream while it normalises.
+//
+// Tensor parallelism is Megatron style: q/k/v, gate/up and lm_head are split by output rows
+// (heads, intermediate units, vocabulary), o_proj/down by input columns, with one allreduce after
+// each row-parallel GEMM (NCCL over NVLink, loaded lazily so that single-GPU use needs no NCCL).
+#include <dlfcn.h>
+#include <math.h>
+#include <string.h>
+
+#include <algorithm>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "ctx.h"
+
+using namespace rb;
+
+namespace {
+
+// ---- the handful of NCCL entry points the driver needs, resolved at rb_model_tp_init
+struct UniqueId { char bytes[128]; };  // same layout as ncclUniqueId, which NCCL takes by value
+struct Nccl {
+  void* lib = nullptr;
+  int (*GetUniqueId)(void*) = nullptr;
+  int (*CommInitRank)(void**, int, UniqueId, int) = nullptr;
+  int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+  int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
+  int (*CommDestroy)(void*) = nullptr;
+  const char* (*GetErrorString)(int) = nullptr;
+};
+constexpr int kNcclFloat32 = 7, kNcclBfloat16 = 9, kNcclSum = 0, kNcclUint8 = 1;
+
+Nccl& nccl() {
+  static Nccl n;
+  return n;
+}
+
+int nccl_load() {
+  Nccl& n = nccl();
+  if (n.lib) return RB_OK;
+  void* lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+  if (!lib) return fail(RB_ERR_UNIMPLEMENTED, "tensor parallelism needs libnccl.so.2: %s", dlerror());
+  n.GetUniqueId = (int (*)(void*))dlsym(lib, "ncclGetUniqueId");
+  n.CommInitRank = (int (*)(void**, int, UniqueId, int))dlsym(lib, "ncclCommInitRank");
+  n.AllReduce = (int (*)(const void*, void*, size_t, int, int, void*, cudaStream_t))dlsym(lib, "ncclAllReduce");
+  n.AllGather = (int (*)(const void*, void*, size_t, int, void*, cudaStream_t))dlsym(lib, "ncclAllGather");
+  n.CommDestroy = (int (*)(void*))dlsym(lib, "ncclCommDestroy");
+  n.GetErrorString = (const char* (*)(int))dlsym(lib, "ncclGetErrorString");
+  if (!n.GetUniqueId || !n.CommInitRank || !n.AllReduce || !n.AllGather || !n.CommDestroy || !n.GetErrorString)
+    return fail(RB_ERR_UNIMPLEMENTED, "libnccl.so.2 lacks an expected symbol");
+  n.lib = lib;
+  return RB_OK;
+}
+
+#define RB_NCCL(expr)                                                                                   \
+  do {                                                                                                  \
+    int _r = (expr);                                                                                    \
+    if (_r != 0) return fail(RB_ERR_CUDA, "%s failed: %s", #expr, nccl().GetErrorString(_r));           \
+  } while (0)
+
+// One rectangular piece of a reference parameter and where it lands in this rank's buffers.
+struct Piece {
+  int64_t src_row0, rows, src_col0, cols;
+  void* dst;
+  int64_t dst_ld;  // elements
+};
+struct ParamSpec {
+  int64_t rows, cols;  // full shape of the reference parameter (cols = 1 for vectors)
+  int rank;            // 1 or 2
+  std::vector<Piece> pieces;
+  bool loaded = false;
+};
+
+struct LayerW {
+  void *qkv = nullptr, *qkv_b = nullptr;
+  void *o = nullptr, *o_b = nullptr;
+  void *gate = nullptr, *up = nullptr, *fc1_b = nullptr;  // phi2: gate = fc1
+  void *down = nullptr, *down_b = nullptr;                // phi2: down = fc2
+  void *ln1_w = nullptr, *ln1_b = nullptr, *ln2_w = nullptr;
+};
+
+template <typename S, typename T>
+__global__ void copy_cast_2d_kernel(const S* __restrict__ src, int64_t src_ld, T* __restrict__ dst, int64_t dst_ld,
+                                    int64_t rows, int64_t cols) {
+  const int64_t n = rows * cols;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / cols, c = i % cols;
+    dst[r * dst_ld + c] = Cvt<T>::from_f(Cvt<S>::to_f(src[r * src_ld + c]));
+  }
+}
+
+__global__ void set_lens_kernel(int32_t* lens, int n, int len) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) lens[i] = len;
+}
+
+// out[b, r*vl + j] = gathered[r, b, j]  (vocabulary shards back into rows of logits)
+template <typename T>
+__global__ void unshard_logits_kernel(const T* __restrict__ g, T* __restrict__ out, int tp, int batch, int vl) {
+  const int64_t n = (int64_t)tp * batch * vl;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int j = (int)(i % vl);
+    const int b = (int)((i / vl) % batch);
+    const int r = (int)(i / ((int64_t)vl * batch));
+    out[((int64_t)b * tp + r) * vl + j] = g[i];
+  }
+}
+
+struct Pending {  // terms still to be added to the residual stream
+  const float* acc = nullptr;
+  int n_acc = 0;
+  const void* acc_bias = nullptr;
+  const void* add = nullptr;
+  bool any() const { return (acc && n_acc > 0) || add; }
+};
+
+}  // namespace
+
+struct rb_model {
+  rb_ctx* ctx = nullptr;
+  rb_model_config cfg{};
+  int d = 0, nq_l = 0, nkv_l = 0, nqkv_l = 0, inter_l = 0, vocab_l = 0;
+  std::vector<int> q_head_src;  // global q head of local head j, or -1 for padding
+  int kv_head0 = 0;             // first global kv head of this rank
+  size_t es = 2;
+  std::vector<LayerW> layers;
+  void *embed = nullptr, *norm_w = nullptr, *norm_b = nullptr, *lm_head = nullptr, *lm_head_b = nullptr;
+  float *rope_cos = nullptr, *rope_sin = nullptr;
+  rb_kv_cache* cache = nullptr;
+  std::vector<void*> owned;
+  std::vector<std::string> names;
+  std::map<std::string, ParamSpec> params;
+  int64_t param_bytes = 0;
+  // workspace
+  uint32_t* ids = nullptr;
+  void *h = nullptr, *xn = nullptr, *tmp = nullptr, *qkv = nullptr, *q = nullptr, *attn = nullptr, *act = nullptr;
+  void *last_h = nullptr, *logits = nullptr, *logits_g = nullptr;
+  uint32_t* next_ids = nullptr;
+  float* scratch = nullptr;  // split-K partials
+  size_t scratch_floats = 0;
+  void* comm = nullptr;
+};
+
+namespace {
+
+int dev_alloc(rb_model* m, size_t bytes, void** out, bool zero) {
+  RB_TRY(rb_malloc(m->ctx, bytes, out));
+  m->owned.push_back(*out);
+  if (zero && bytes) RB_CUDA(cudaMemsetAsync(*out, 0, bytes, m->ctx->stream));
+  return RB_OK;
+}
+
+int weight_alloc(rb_model* m, int64_t elems, void** out) {
+  m->param_bytes += elems * (int64_t)m->es;
+  return dev_alloc(m, (size_t)elems * m->es, out, true);
+}
+
+void add_param(rb_model* m, const std::string& name, int64_t rows, int64_t cols, int rank, std::vector<Piece> pieces) {
+  ParamSpec s;
+  s.rows = rows; s.cols = cols; s.rank = rank; s.pieces = std::move(pieces);
+  m->names.push_back(name);
+  m->params[name] = std::move(s);
+}
+
+int norm_kind(const rb_model* m) {
+  return m->cfg.arch == RB_ARCH_PHI2 ? RB_NORM_LAYER : m->cfg.arch == RB_ARCH_GEMMA ? RB_NORM_RMS_ONE_PLUS : RB_NORM_RMS;
+}
+
+int allreduce(rb_model* m, void* buf, size_t count) {
+  RB_NCCL(nccl().AllReduce(buf, buf, count, m->cfg.dtype == RB_BF16 ? kNcclBfloat16 : kNcclFloat32, kNcclSum, m->comm,
+                           m->ctx->stream));
+  return RB_OK;
+}
+
+// v = h + pending ; h = v ; out = norm(v)   (out may be NULL: only fold the pending terms)
+int norm_point(rb_model* m, Pending& pend, const void* w, const void* b, int64_t rows, void* out) {
+  if (!out && !pend.any()) return RB_OK;
+  RB_TRY(rb_norm(m->ctx, norm_kind(m), m->h, pend.add, pend.acc, pend.n_acc, pend.acc_bias, w, b,
+                 (float)m->cfg.norm_eps, rows, m->cfg.hidden_size, out, pend.any() ? m->h : nullptr, m->cfg.dtype));
+  pend = Pending();
+  return RB_OK;
+}
+
+bool use_partials(rb_model* m, int64_t rows, int64_t n, int64_t k, int* splits) {
+  if (m->cfg.dtype != RB_BF16 || rows > 256) return false;
+  const int s = rb_linear_pick_splits(m->ctx, rows, n, k);
+  if (s <= 1 || (size_t)s * rows * n > m->scratch_floats) return false;
+  *splits = s;
+  return true;
+}
+
+// h += x . W^T + bias, either at once (epilogue residual) or left pending for the next norm_point.
+int linear_into_residual(rb_model* m, Pending& pend, const void* x, const void* w, const void* bias, int64_t rows,
+                         int64_t n, int64_t k) {
+  if (pend.any()) RB_TRY(norm_point(m, pend, nullptr, nullptr, rows, nullptr));
+  const void* b = (m->cfg.tp_rank == 0) ? bias : nullptr;  // a row-parallel bias is added once
+  if (m->cfg.tp_size > 1) {
+    RB_TRY(rb_linear(m->ctx, x, w, b, nullptr, m->tmp, rows, n, k, RB_ACT_NONE, m->cfg.dtype));
+    RB_TRY(allreduce(m, m->tmp, (size_t)rows * n));
+    pend.add = m->tmp;
+    return RB_OK;
+  }
+  int s = 1;
+  if (use_partials(m, rows, n, k, &s)) {
+    RB_TRY(rb_linear_partials(m->ctx, x, w, m->scratch, rows, n, k, s));
+    pend.acc = m->scratch; pend.n_acc = s; pend.acc_bias = b;
+    return RB_OK;
+  }
+  return rb_linear(m->ctx, x, w, b, m->h, m->h, rows, n, k, RB_ACT_NONE, m->cfg.dtype);
+}
+
+int forward_impl(rb_model* m, const uint32_t* tokens, int batch, int seq, int pos, void* logits_out) {
+  const rb_model_config& c = m->cfg;
+  rb_ctx* ctx = m->ctx;
+  const int64_t rows = (int64_t)batch * seq;
+  const int H = c.hidden_size, d = m->d;
+  RB_REQUIRE(batch > 0 && batch <= c.max_batch, "forward: batch %d exceeds max_batch %d", batch, c.max_batch);
+  RB_REQUIRE(seq > 0 && rows <= c.max_tokens, "forward: %lld tokens exceed max_tokens %d", (long long)rows, c.max_tokens);
+  RB_REQUIRE(pos >= 0 && pos + seq <= m->cache->max_seq && pos + seq <= c.max_position_embeddings,
+             "forward: position %d + %d exceeds the cache / rotary table capacity", pos, seq);
+  for (int b = 0; b < batch; ++b)
+    RB_REQUIRE(m->cache->host_lens[b] == pos, "forward: seqlen_offset %d differs from the cached length %d of sequence %d",
+               pos, m->cache->host_lens[b], b);
+  // device-side lengths after this call's tokens are appended
+  set_lens_kernel<<<(batch + 127) / 128, 128, 0, ctx->stream>>>(m->cache->seq_lens, batch, pos + seq);
+  ctx->launches++;
+  for (int b = 0; b < batch; ++b) m->cache->host_lens[b] = pos + seq;
+
+  const float emb_scale = c.arch == RB_ARCH_GEMMA ? sqrtf((float)H) : 1.0f;  // gemma.rs:379
+  RB_TRY(rb_embed_gather(ctx, m->embed, c.dtype, c.vocab_size, H, tokens, rows, emb_scale, m->h));
+
+  const float scale = 1.0f / sqrtf((float)d);
+  const int L = c.num_hidden_layers;
+  Pending pend;
+  for (int l = 0; l < L; ++l) {
+    const LayerW& w = m->layers[l];
+    // input_layernorm, folding what the previous layer left pending
+    RB_TRY(norm_point(m, pend, w.ln1_w, w.ln1_b, rows, m->xn));
+    // q/k/v projection -> rope -> cache
+    int s = 1;
+    if (use_partials(m, rows, m->nqkv_l, H, &s)) {
+      RB_TRY(rb_linear_partials(ctx, m->xn, w.qkv, m->scratch, rows, m->nqkv_l, H, s));
+      RB_TRY(rb_rope_kv_append(ctx, nullptr, m->scratch, s, w.qkv_b, m->rope_cos, m->rope_sin, c.rotary_dim, batch, seq,
+                               m->nq_l, m->cache, l, m->q, c.dtype));
+    } else {
+      RB_TRY(rb_linear(ctx, m->xn, w.qkv, w.qkv_b, nullptr, m->qkv, rows, m->nqkv_l, H, RB_ACT_NONE, c.dtype));
+      RB_TRY(rb_rope_kv_append(ctx, m->qkv, nullptr, 0, nullptr, m->rope_cos, m->rope_sin, c.rotary_dim, batch, seq,
+                               m->nq_l, m->cache, l, m->q, c.dtype));
+    }
+    RB_TRY(rb_attention(ctx, m->q, m->cache, l, batch, seq, m->nq_l, scale, m->attn, c.dtype));
+    RB_TRY(linear_into_residual(m, pend, m->attn, w.o, w.o_b, rows, H, (int64_t)m->nq_l * d));
+    if (c.arch == RB_ARCH_PHI2) {
+      // parallel block (phi2.rs:293-299): the MLP reads the same normed input as the attention
+      RB_TRY(rb_linear(ctx, m->xn, w.gate, w.fc1_b, nullptr, m->act, rows, m->inter_l, H, c.hidden_act, c.dtype));
+    } else {
+      RB_TRY(norm_point(m, pend, w.ln2_w, nullptr, rows, m->xn));  // post_attention_layernorm
+      RB_TRY(rb_gated_linear(ctx, m->xn, w.gate, w.up, m->act, rows, m->inter_l, H, c.hidden_act, c.dtype));
+    }
+    RB_TRY(linear_into_residual(m, pend, m->act, w.down, w.down_b, rows, H, m->inter_l));
+  }
+  RB_TRY(norm_point(m, pend, nullptr, nullptr, rows, nullptr));  // fold the last layer's output
+
+  // logits for the last position only (qwen2.rs:356-358; phi2.rs:345-346 normalises every row first,
+  // which is the same thing for a row-wise norm)
+  const void* last = m->h;
+  if (seq > 1) {
+    RB_CUDA(cudaMemcpy2DAsync(m->last_h, (size_t)H * m->es, (const char*)m->h + (size_t)(seq - 1) * H * m->es,
+                              (size_t)seq * H * m->es, (size_t)H * m->es, batch, cudaMemcpyDeviceToDevice, ctx->stream));
+    last = m->last_h;
+  }
+  RB_TRY(rb_norm(ctx, norm_kind(m), last, nullptr, nullptr, 0, nullptr, m->norm_w, m->norm_b, (float)c.norm_eps, batch, H,
+                 m->xn, nullptr, c.dtype));
+  void* head_w = m->lm_head ? m->lm_head : m->embed;
+  if (c.tp_size == 1) {
+    RB_TRY(rb_linear(ctx, m->xn, head_w, m->lm_head_b, nullptr, m->logits, batch, m->vocab_l, H, RB_ACT_NONE, c.dtype));
+  } else {
+    RB_TRY(rb_linear(ctx, m->xn, head_w, m->lm_head_b, nullptr, m->logits_g, batch, m->vocab_l, H, RB_ACT_NONE, c.dtype));
+    void* gathered = (char*)m->logits_g + (size_t)batch * m->vocab_l * m->es;
+    RB_NCCL(nccl().AllGather(m->logits_g, gathered, (size_t)batch * m->vocab_l * m->es, kNcclUint8, m->comm, ctx->stream));
+    const int64_t n = (int64_t)c.tp_size * batch * m->vocab_l;
+    const int blocks = (int)std::min<int64_t>((n + 255) / 256, 4096);
+    if (c.dtype == RB_BF16)
+      unshard_logits_kernel<__nv_bfloat16><<<blocks, 256, 0, ctx->stream>>>((const __nv_bfloat16*)gathered,
+                                                                           (__nv_bfloat16*)m->logits, c.tp_size, batch,
+                                                                           m->vocab_l);
+    else
+      unshard_logits_kernel<float><<<blocks, 256, 0, ctx->stream>>>((const float*)gathered, (float*)m->logits, c.tp_size,
+                                                                   batch, m->vocab_l);
+    ctx->launches++;
+  }
+  if (logits_out && logits_out != m->logits)
+    RB_CUDA(cudaMemcpyAsync(logits_out, m->logits, (size_t)batch * c.vocab_size * m->es, cudaMemcpyDeviceToDevice,
+                            ctx->stream));
+  return RB_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t rb_tp_unique_id(void* out128) {
+  RB_REQUIRE(out128, "rb_tp_unique_id: null output");
+  RB_TRY(nccl_load());
+  RB_NCCL(nccl().GetUniqueId(out128));
+  return RB_OK;
+}
+
+extern "C" int32_t rb_model_tp_init(rb_model* m, const void* id, int32_t id_bytes) {
+  RB_REQUIRE(m && id && id_bytes == 128, "rb_model_tp_init: expects a 128-byte ncclUniqueId");
+  if (m->cfg.tp_size <= 1) return RB_OK;
+  RB_TRY(nccl_load());
+  UniqueId u;
+  memcpy(u.bytes, id, 128);
+  RB_CUDA(cudaSetDevice(m->ctx->device));
+  RB_NCCL(nccl().CommInitRank(&m->comm, m->cfg.tp_size, u, m->cfg.tp_rank));
+  return RB_OK;
+}
+
+extern "C" int32_t rb_model_create(rb_ctx* ctx, const rb_model_config* cfg, rb_model** out) {
+  RB_REQUIRE(ctx && cfg && out, "rb_model_create: null argument");
+  const rb_model_config& c = *cfg;
+  RB_REQUIRE(c.arch >= RB_ARCH_QWEN2 && c.arch <= RB_ARCH_GEMMA, "rb_model_create: unknown arch %d", c.arch);
+  RB_REQUIRE(c.dtype == RB_BF16 || c.dtype == RB_F32, "rb_model_create: dtype %d unsupported", c.dtype);
+  RB_REQUIRE(c.hidden_size > 0 && c.num_attention_heads > 0 && c.hidden_size % c.num_attention_heads == 0,
+             "rb_model_create: hidden_size must divide by num_attention_heads");
+  RB_REQUIRE(c.num_key_value_heads > 0 && c.num_attention_heads % c.num_key_value_heads == 0,
+             "rb_model_create: num_attention_heads must divide by num_key_value_heads");
+  RB_REQUIRE(c.tp_size >= 1 && c.tp_rank >= 0 && c.tp_rank < c.tp_size, "rb_model_create: bad tensor-parallel rank");
+  RB_REQUIRE(c.max_batch > 0 && c.max_seq > 0 && c.max_tokens >= c.max_batch, "rb_model_create: bad capacities");
+  const int tp = c.tp_size, rank = c.tp_rank;
+  const int nq = c.num_attention_heads, nkv = c.num_key_value_heads, G = nq / nkv;
+  RB_REQUIRE(c.intermediate_size % tp == 0 && c.vocab_size % tp == 0,
+             "rb_model_create: intermediate_size and vocab_size must divide by tp_size");
+  RB_REQUIRE((tp <= nkv && nkv % tp == 0) || (tp > nkv && tp % nkv == 0),
+             "rb_model_create: tp_size %d and %d KV heads do not divide either way", tp, nkv);
+
+  rb_model* m = new rb_model();
+  m->ctx = ctx;
+  m->cfg = c;
+  m->d = c.hidden_size / nq;
+  m->es = dtype_size(c.dtype);
+  const int d = m->d, H = c.hidden_size;
+  // ---- head assignment
+  if (tp <= nkv) {
+    m->nkv_l = nkv / tp;
+    m->kv_head0 = rank * m->nkv_l;
+    m->nq_l = m->nkv_l * G;
+    for (int j = 0; j < m->nq_l; ++j) m->q_head_src.push_back(m->kv_head0 * G + j);
+  } else {
+    // more ranks than KV heads: `rpk` ranks share one KV head, each takes ceil(G / rpk) of its query
+    // heads; the last of them may carry zero-weight padding heads (their o_proj columns are zero)
+    const int rpk = tp / nkv, qpr = (G + rpk - 1) / rpk;
+    m->nkv_l = 1;
+    m->kv_head0 = rank / rpk;
+    m->nq_l = qpr;
+    const int sub = rank % rpk;
+    for (int j = 0; j < qpr; ++j) {
+      const int within = sub * qpr + j;
+      m->q_head_src.push_back(within < G ? m->kv_head0 * G + within : -1);
+    }
+  }
+  m->nqkv_l = (m->nq_l + 2 * m->nkv_l) * d;
+  m->inter_l = c.intermediate_size / tp;
+  m->vocab_l = c.vocab_size / tp;
+  const int I = c.intermediate_size, Il = m->inter_l, V = c.vocab_size, Vl = m->vocab_l;
+  const bool phi2 = c.arch == RB_ARCH_PHI2, phi3 = c.arch == RB_ARCH_PHI3;
+  const bool qkv_bias = c.arch == RB_ARCH_QWEN2 || phi2;
+
+  int st = RB_OK;
+  auto A = [&](int64_t elems, void** p) { if (st == RB_OK) st = weight_alloc(m, elems, p); };
+  auto P = [&](void* base, int64_t elem_off) { return (void*)((char*)base + elem_off * (int64_t)m->es); };
+
+  A((int64_t)V * H, &m->embed);
+  A(H, &m->norm_w);
+  if (phi2) A(H, &m->norm_b);
+  const bool own_head = !(c.arch == RB_ARCH_GEMMA || c.tie_word_embeddings);
+  if (own_head || tp > 1) A((int64_t)Vl * H, &m->lm_head);
+  if (phi2) A(Vl, &m->lm_head_b);
+  m->layers.resize(c.num_hidden_layers);
+  for (auto& w : m->layers) {
+    A((int64_t)m->nqkv_l * H, &w.qkv);
+    if (qkv_bias) A(m->nqkv_l, &w.qkv_b);
+    A((int64_t)H * m->nq_l * d, &w.o);
+    if (phi2) A(H, &w.o_b);
+    A((int64_t)Il * H, &w.gate);
+    if (!phi2) A((int64_t)Il * H, &w.up); else A(Il, &w.fc1_b);
+    A((int64_t)H * Il, &w.down);
+    if (phi2) A(H, &w.down_b);
+    A(H, &w.ln1_w);
+    if (phi2) A(H, &w.ln1_b); else A(H, &w.ln2_w);
+  }
+  if (st != RB_OK) { rb_model_destroy(m); return st; }
+
+  // ---- parameter registry (names per the derive rule, rai-core/src/nn.rs:256-269)
+  {
+    std::vector<Piece> pe{{0, V, 0, H, m->embed, H}};
+    if (!own_head && tp > 1) pe.push_back({(int64_t)rank * Vl, Vl, 0, H, m->lm_head, H});  // tied head, vocab shard
+    add_param(m, "model.embed_tokens.weight", V, H, 2, pe);
+  }
+  const std::string fnorm = phi2 ? "model.final_layernorm" : "model.norm";
+  add_param(m, fnorm + ".weight", H, 1, 1, {{0, H, 0, 1, m->norm_w, 1}});
+  if (phi2) add_param(m, fnorm + ".bias", H, 1, 1, {{0, H, 0, 1, m->norm_b, 1}});
+  if (own_head) {
+    add_param(m, "lm_head.weight", V, H, 2, {{(int64_t)rank * Vl, Vl, 0, H, m->lm_head, H}});
+    if (phi2) add_param(m, "lm_head.bias", V, 1, 1, {{(int64_t)rank * Vl, Vl, 0, 1, m->lm_head_b, 1}});
+  }
+  for (int l = 0; l < c.num_hidden_layers; ++l) {
+    LayerW& w = m->layers[l];
+    const std::string pre = "model.layers." + std::to_string(l) + ".";
+    // fused qkv rows: [local q heads | local k heads | local v heads]
+    auto head_pieces = [&](int64_t src_head_row0, bool is_q, int64_t dst_row0, void* dst, int64_t cols, int64_t ld) {
+      std::vector<Piece> ps;
+      if (is_q) {
+        for (int j = 0; j < m->nq_l; ++j)
+          if (m->q_head_src[j] >= 0)
+            ps.push_back({src_head_row0 + (int64_t)m->q_head_src[j] * d, d, 0, cols, P(dst, (dst_row0 + (int64_t)j * d) * ld), ld});
+      } else {
+        ps.push_back({src_head_row0 + (int64_t)m->kv_head0 * d, (int64_t)m->nkv_l * d, 0, cols, P(dst, dst_row0 * ld), ld});
+      }
+      return ps;
+    };
+    const int64_t kq = (int64_t)m->nq_l * d, kk = (int64_t)m->nkv_l * d;
+    if (phi3) {
+      std::vector<Piece> ps = head_pieces(0, true, 0, w.qkv, H, H);
+      auto pk = head_pieces((int64_t)nq * d, false, kq, w.qkv, H, H);
+      auto pv = head_pieces((int64_t)(nq + nkv) * d, false, kq + kk, w.qkv, H, H);
+      ps.insert(ps.end(), pk.begin(), pk.end());
+      ps.insert(ps.end(), pv.begin(), pv.end());
+      add_param(m, pre + "self_attn.qkv_proj.weight", (int64_t)(nq + 2 * nkv) * d, H, 2, ps);
+    } else {
+      add_param(m, pre + "self_attn.q_proj.weight", (int64_t)nq * d, H, 2, head_pieces(0, true, 0, w.qkv, H, H));
+      add_param(m, pre + "self_attn.k_proj.weight", (int64_t)nkv * d, H, 2, head_pieces(0, false, kq, w.qkv, H, H));
+      add_param(m, pre + "self_attn.v_proj.weight", (int64_t)nkv * d, H, 2, head_pieces(0, false, kq + kk, w.qkv, H, H));
+      if (qkv_bias) {
+        add_param(m, pre + "self_attn.q_proj.bias", (int64_t)nq * d, 1, 1, head_pieces(0, true, 0, w.qkv_b, 1, 1));
+        add_param(m, pre + "self_attn.k_proj.bias", (int64_t)nkv * d, 1, 1, head_pieces(0, false, kq, w.qkv_b, 1, 1));
+        add_param(m, pre + "self_attn.v_proj.bias", (int64_t)nkv * d, 1, 1, head_pieces(0, false, kq + kk, w.qkv_b, 1, 1));
+      }
+    }
+    {  // o_proj / dense: input columns follow the local query heads
+      std::vector<Piece> ps;
+      for (int j = 0; j < m->nq_l; ++j)
+        if (m->q_head_src[j] >= 0)
+          ps.push_back({0, H, (int64_t)m->q_head_src[j] * d, d, P(w.o, (int64_t)j * d), kq});
+      add_param(m, pre + (phi2 ? "self_attn.dense.weight" : "self_attn.o_proj.weight"), H, (int64_t)nq * d, 2, ps);
+      if (phi2) add_param(m, pre + "self_attn.dense.bias", H, 1, 1, {{0, H, 0, 1, w.o_b, 1}});
+    }
+    if (phi3) {
+      add_param(m, pre + "mlp.gate_up_proj.weight", 2 * (int64_t)I, H, 2,
+                {{(int64_t)rank * Il, Il, 0, H, w.gate, H}, {(int64_t)I + (int64_t)rank * Il, Il, 0, H, w.up, H}});
+      add_param(m, pre + "mlp.down_proj.weight", H, I, 2, {{0, H, (int64_t)rank * Il, Il, w.down, Il}});
+    } else if (phi2) {
+      add_param(m, pre + "mlp.fc1.weight", I, H, 2, {{(int64_t)rank * Il, Il, 0, H, w.gate, H}});
+      add_param(m, pre + "mlp.fc1.bias", I, 1, 1, {{(int64_t)rank * Il, Il, 0, 1, w.fc1_b, 1}});
+      add_param(m, pre + "mlp.fc2.weight", H, I, 2, {{0, H, (int64_t)rank * Il, Il, w.down, Il}});
+      add_param(m, pre + "mlp.fc2.bias", H, 1, 1, {{0, H, 0, 1, w.down_b, 1}});
+    } else {
+      add_param(m, pre + "mlp.gate_proj.weight", I, H, 2, {{(int64_t)rank * Il, Il, 0, H, w.gate, H}});
+      add_param(m, pre + "mlp.up_proj.weight", I, H, 2, {{(int64_t)rank * Il, Il, 0, H, w.up, H}});
+      add_param(m, pre + "mlp.down_proj.weight", H, I, 2, {{0, H, (int64_t)rank * Il, Il, w.down, Il}});
+    }
+    add_param(m, pre + "input_layernorm.weight", H, 1, 1, {{0, H, 0, 1, w.ln1_w, 1}});
+    if (phi2) add_param(m, pre + "input_layernorm.bias", H, 1, 1, {{0, H, 0, 1, w.ln1_b, 1}});
+    else add_param(m, pre + "post_attention_layernorm.weight", H, 1, 1, {{0, H, 0, 1, w.ln2_w, 1}});
+  }
+
+  // ---- rotary tables, cache, workspace
+  const int half = c.rotary_dim / 2;
+  const int recipe = phi2 ? 1 : phi3 ? 2 : 0;
+  auto W = [&](size_t bytes, void** p) { if (st == RB_OK) st = dev_alloc(m, bytes, p, false); };
+  W((size_t)c.max_position_embeddings * half * sizeof(float), (void**)&m->rope_cos);
+  W((size_t)c.max_position_embeddings * half * sizeof(float), (void**)&m->rope_sin);
+  if (st == RB_OK) st = rb_rope_tables(ctx, recipe, c.rotary_dim, c.max_position_embeddings, c.rope_theta, m->rope_cos, m->rope_sin);
+  if (st == RB_OK) st = rb_kv_cache_create(ctx, c.num_hidden_layers, m->nkv_l, d, c.max_batch, c.max_seq, c.dtype, &m->cache);
+  const size_t MT = c.max_tokens;
+  W(MT * sizeof(uint32_t), (void**)&m->ids);
+  W(MT * H * m->es, &m->h);
+  W(MT * H * m->es, &m->xn);
+  if (tp > 1) W(MT * H * m->es, &m->tmp);
+  W(MT * m->nqkv_l * m->es, &m->qkv);
+  W(MT * m->nq_l * d * m->es, &m->q);
+  W(MT * m->nq_l * d * m->es, &m->attn);
+  W(MT * Il * m->es, &m->act);
+  W((size_t)c.max_batch * H * m->es, &m->last_h);
+  W((size_t)c.max_batch * V * m->es, &m->logits);
+  if (tp > 1) W((size_t)c.max_batch * Vl * m->es * (tp + 1), &m->logits_g);
+  W((size_t)c.max_batch * sizeof(uint32_t), (void**)&m->next_ids);
+  if (c.dtype == RB_BF16 && tp == 1) {
+    // split-K scratch: up to 16 slabs of min(max_tokens, 256) rows of the widest split-K output
+    const size_t rows = std::min<size_t>(MT, 256);
+    m->scratch_floats = (size_t)16 * rows * std::max(m->nqkv_l, H);
+    W(m->scratch_floats * sizeof(float), (void**)&m->scratch);
+  }
+  if (st != RB_OK) { rb_model_destroy(m); return st; }
+  RB_CUDA(cudaStreamSynchronize(ctx->stream));
+  *out = m;
+  return RB_OK;
+}
+
+extern "C" int32_t rb_model_destroy(rb_model* m) {
+  if (!m) return RB_OK;
+  cudaStreamSynchronize(m->ctx->stream);
+  if (m->comm && nccl().CommDestroy) nccl().CommDestroy(m->comm);
+  if (m->cache) rb_kv_cache_destroy(m->cache);
+  for (void* p : m->owned) rb_free(m->ctx, p);
+  delete m;
+  return RB_OK;
+}
+
+extern "C" int32_t rb_model_param_count(rb_model* m) { return m ? (int32_t)m->names.size() : 0; }
+extern "C" const char* rb_model_param_name(rb_model* m, int32_t i) {
+  return (m && i >= 0 && i < (int32_t)m->names.size()) ? m->names[i].c_str() : nullptr;
+}
+extern "C" int64_t rb_model_param_bytes(rb_model* m) { return m ? m->param_bytes : 0; }
+extern "C" rb_kv_cache* rb_model_kv_cache(rb_model* m) { return m ? m->cache : nullptr; }
+
+template <typename S>
+static int copy_pieces(rb_model* m, const ParamSpec& sp, const S* src_dev) {
+  for (const Piece& pc : sp.pieces) {
+    const int64_t n = pc.rows * pc.cols;
+    if (n == 0) continue;
+    const int blocks = (int)std::min<int64_t>((n + 255) / 256, 8192);
+    const S* src = src_dev + pc.src_row0 * sp.cols + pc.src_col0;
+    if (m->cfg.dtype == RB_BF16)
+      copy_cast_2d_kernel<S, __nv_bfloat16><<<blocks, 256, 0, m->ctx->stream>>>(src, sp.cols, (__nv_bfloat16*)pc.dst,
+                                                                                pc.dst_ld, pc.rows, pc.cols);
+    else
+      copy_cast_2d_kernel<S, float><<<blocks, 256, 0, m->ctx->stream>>>(src, sp.cols, (float*)pc.dst, pc.dst_ld, pc.rows,
+                                                                        pc.cols);
+    m->ctx->launches++;
+    RB_TRY(launch_status("copy_cast_2d"));
+  }
+  return RB_OK;
+}
+
+extern "C" int32_t rb_model_load_param(rb_model* m, const char* name, const void* data, int32_t on_device,
+                                       int32_t src_dtype, int32_t rank, const int64_t* shape) {
+  RB_REQUIRE(m && name && data && shape, "rb_model_load_param: null argument");
+  auto it = m->params.find(name);
+  if (it == m->params.end()) return fail(RB_ERR_PARAM, "parameter '%s' is not part of this model", name);
+  ParamSpec& sp = it->second;
+  RB_REQUIRE(src_dtype == RB_F32 || src_dtype == RB_BF16, "rb_model_load_param: source dtype %d unsupported", src_dtype);
+  const int64_t rows = shape[0], cols = rank >= 2 ? shape[1] : 1;
+  if (rank != sp.rank || rows != sp.rows || cols != sp.cols)
+    return fail(RB_ERR_SHAPE, "parameter '%s': got shape [%lld, %lld] (rank %d), expected [%lld, %lld] (rank %d)", name,
+                (long long)rows, (long long)cols, rank, (long long)sp.rows, (long long)sp.cols, sp.rank);
+  const size_t bytes = (size_t)rows * cols * dtype_size(src_dtype);
+  const void* src = data;
+  void* staging = nullptr;
+  if (!on_device) {
+    RB_TRY(rb_malloc(m->ctx, bytes, &staging));
+    int st = rb_upload(m->ctx, staging, data, bytes);
+    if (st != RB_OK) { rb_free(m->ctx, staging); return st; }
+    src = staging;
+  }
+  int st = src_dtype == RB_F32 ? copy_pieces<float>(m, sp, (const float*)src)
+                               : copy_pieces<__nv_bfloat16>(m, sp, (const __nv_bfloat16*)src);
+  if (staging) {
+    cudaStreamSynchronize(m->ctx->stream);
+    cudaFree(staging);
+  }
+  if (st == RB_OK) sp.loaded = true;
+  return st;
+}
+
+extern "C" int32_t rb_model_finalize(rb_model* m) {
+  RB_REQUIRE(m, "rb_model_finalize: null model");
+  for (const std::string& n : m->names)
+    if (!m->params[n].loaded) return fail(RB_ERR_PARAM, "parameter '%s' was never loaded", n.c_str());
+  RB_CUDA(cudaStreamSynchronize(m->ctx->stream));
+  return RB_OK;
+}
+
+extern "C" int32_t rb_model_clear_kv_cache(rb_model* m) {
+  RB_REQUIRE(m, "rb_model_clear_kv_cache: null model");
+  return rb_kv_cache_reset(m->cache);
+}
+
+extern "C" int32_t rb_model_forward(rb_model* m, const uint32_t* tokens_dev, int32_t batch, int32_t seq, int32_t pos,
+                                    void* logits_dev) {
+  RB_REQUIRE(m && tokens_dev, "rb_model_forward: null argument");
+  return forward_impl(m, tokens_dev, batch, seq, pos, logits_dev);
+}
+
+extern "C" int32_t rb_model_generate_step(rb_model* m, const uint32_t* tokens_host, int32_t batch, int32_t seq,
+                                          int32_t pos, uint32_t* next_host) {
+  RB_REQUIRE(m && tokens_host && next_host, "rb_model_generate_step: null argument");
+  RB_REQUIRE(batch > 0 && seq > 0 && (int64_t)batch * seq <= m->cfg.max_tokens, "rb_model_generate_step: bad sizes");
+  rb_ctx* ctx = m->ctx;
+  RB_CUDA(cudaMemcpyAsync(m->ids, tokens_host, (size_t)batch * seq * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream));
+  RB_TRY(forward_impl(m, m->ids, batch, seq, pos, nullptr));
+  RB_TRY(rb_argmax_rows(ctx, m->logits, m->cfg.dtype, batch, m->cfg.vocab_size, m->next_ids));
+  RB_CUDA(cudaMemcpyAsync(next_host, m->next_ids, (size_t)batch * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+  return rb_sync(ctx);
+}
+
+extern "C" int32_t rb_model_decode_loop(rb_model* m, const uint32_t* tokens_dev, int32_t batch, int32_t pos,
+                                        int32_t steps, uint32_t* out_dev) {
+  RB_REQUIRE(m && tokens_dev && out_dev, "rb_model_decode_loop: null argument");
+  const uint32_t* cur = tokens_dev;
+  for (int i = 0; i < steps; ++i) {
+    RB_TRY(forward_impl(m, cur, batch, 1, pos + i, nullptr));
+    RB_TRY(rb_argmax_rows(m->ctx, m->logits, m->cfg.dtype, batch, m->cfg.vocab_size, out_dev + (size_t)i * batch));
+    cur = out_dev + (size_t)i * batch;
+  }
+  return RB_OK;
+}
