@@ -77,8 +77,8 @@ typedef struct rb_model rb_model;
  * ====================================================================================== */
 int32_t rb_init(int32_t device, rb_ctx** out);
 int32_t rb_destroy(rb_ctx* ctx);
-/* Use an existing cudaStream_t (for instance the host framework's current stream); NULL = the
- * context's own stream. */
+/* Enqueue on an existing cudaStream_t (for instance the host framework's current stream) instead of
+ * the stream the context created for itself; NULL selects CUDA's default stream. */
 int32_t rb_set_stream(rb_ctx* ctx, void* cuda_stream);
 /* Blocks until the stream is idle, then reports device-side give-ups (RB_ERR_TIMEOUT). */
 int32_t rb_sync(rb_ctx* ctx);
@@ -273,6 +273,15 @@ int32_t rb_model_clear_kv_cache(rb_model* m);
 rb_kv_cache* rb_model_kv_cache(rb_model* m);
 /* Number of kernels the library launched on this context since creation (self-reported count). */
 int64_t rb_launch_count(rb_ctx* ctx);
+/* Per-launch timing for benchmarks (no counterpart in the reference, which has no tracing call
+ * sites): between rb_profile_start and rb_profile_read every kernel launch of the library is
+ * bracketed by CUDA events on the context's stream.  rb_profile_read synchronises, stops profiling
+ * and fills out4 = {launches, total milliseconds, algorithmic bytes, floating-point operations} for
+ * one kernel class (RB_PROF_*). */
+enum { RB_PROF_GEMM = 0, RB_PROF_ATTENTION = 1, RB_PROF_NORM = 2, RB_PROF_ROPE_KV = 3, RB_PROF_EMBED = 4,
+       RB_PROF_ARGMAX = 5, RB_PROF_OTHER = 6, RB_PROF_CLASSES = 7 };
+int32_t rb_profile_start(rb_ctx* ctx);
+int32_t rb_profile_read(rb_ctx* ctx, int32_t kernel_class, double* out4);
 /* Bytes of device memory the model holds for parameters (after sharding). */
 int64_t rb_model_param_bytes(rb_model* m);
 

@@ -67,6 +67,7 @@ extern "C" int32_t rb_destroy(rb_ctx* ctx) {
   if (!ctx) return RB_OK;
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
+  prof_clear(ctx);
   if (ctx->status_dev) cudaFree(ctx->status_dev);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
   delete ctx;
@@ -75,7 +76,7 @@ extern "C" int32_t rb_destroy(rb_ctx* ctx) {
 
 extern "C" int32_t rb_set_stream(rb_ctx* ctx, void* s) {
   RB_REQUIRE(ctx, "rb_set_stream: null context");
-  ctx->stream = s ? (cudaStream_t)s : ctx->own_stream;
+  ctx->stream = (cudaStream_t)s;  // NULL is CUDA's default stream, which torch uses unless told otherwise
   return RB_OK;
 }
 
@@ -94,6 +95,34 @@ extern "C" int32_t rb_sync(rb_ctx* ctx) {
     RB_CUDA(cudaMemset(ctx->status_dev, 0, 4 * sizeof(uint32_t)));
     const int code = -(int)w[0];
     return fail(code, "device-side check failed: code %d at 0x%x (detail %u, %u)", code, w[1], w[2], w[3]);
+  }
+  return RB_OK;
+}
+
+static void prof_clear(rb_ctx* ctx) {
+  for (auto& r : ctx->prof) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+  ctx->prof.clear();
+}
+
+extern "C" int32_t rb_profile_start(rb_ctx* ctx) {
+  RB_REQUIRE(ctx, "rb_profile_start: null context");
+  RB_CUDA(cudaStreamSynchronize(ctx->stream));
+  prof_clear(ctx);
+  ctx->profiling = true;
+  return RB_OK;
+}
+
+extern "C" int32_t rb_profile_read(rb_ctx* ctx, int32_t cls, double* out4) {
+  RB_REQUIRE(ctx && out4, "rb_profile_read: null argument");
+  RB_REQUIRE(cls >= 0 && cls < RB_PROF_CLASSES, "rb_profile_read: unknown kernel class %d", cls);
+  ctx->profiling = false;
+  RB_CUDA(cudaStreamSynchronize(ctx->stream));
+  out4[0] = out4[1] = out4[2] = out4[3] = 0.0;
+  for (auto& r : ctx->prof) {
+    if (r.cls != cls) continue;
+    float ms = 0.f;
+    RB_CUDA(cudaEventElapsedTime(&ms, r.a, r.b));
+    out4[0] += 1.0; out4[1] += ms; out4[2] += r.bytes; out4[3] += r.flops;
   }
   return RB_OK;
 }
@@ -228,6 +257,9 @@ extern "C" int32_t rb_linear(rb_ctx* ctx, const void* x, const void* w, const vo
   GemmArgs a;
   a.x = x; a.w = w; a.bias = bias; a.residual = residual; a.out = out;
   a.m = m; a.n = n; a.k = k; a.act = act;
+  const double es = (double)dtype_size(dtype);
+  ProfScope prof(ctx, RB_PROF_GEMM, es * ((double)n * k + (double)m * k + (double)m * n * (residual ? 2 : 1) + (bias ? n : 0)),
+                 2.0 * m * n * k);
   if (dtype == RB_BF16 && !ctx->debug_simple) return gemm_tc_bf16(ctx, a);
   return gemm_simple(ctx, a, dtype);
 }
@@ -239,6 +271,8 @@ extern "C" int32_t rb_gated_linear(rb_ctx* ctx, const void* x, const void* wg, c
   GemmArgs a;
   a.x = x; a.w = wg; a.w2 = wu; a.out = out;
   a.m = m; a.n = n; a.k = k; a.act = act;
+  const double es = (double)dtype_size(dtype);
+  ProfScope prof(ctx, RB_PROF_GEMM, es * (2.0 * n * k + (double)m * k + (double)m * n), 4.0 * m * n * k);
   if (dtype == RB_BF16 && !ctx->debug_simple) return gemm_tc_bf16(ctx, a);
   return gemm_simple(ctx, a, dtype);
 }
@@ -251,6 +285,7 @@ extern "C" int32_t rb_linear_partials(rb_ctx* ctx, const void* x, const void* w,
   a.x = x; a.w = w; a.out = part;
   a.m = m; a.n = n; a.k = k;
   a.n_split = n_split; a.partials = true;
+  ProfScope prof(ctx, RB_PROF_GEMM, 2.0 * ((double)n * k + (double)m * k) + 4.0 * n_split * m * n, 2.0 * m * n * k);
   if (!ctx->debug_simple) return gemm_tc_bf16(ctx, a);
   return gemm_simple(ctx, a, RB_BF16);
 }
@@ -271,6 +306,15 @@ extern "C" int32_t rb_attention(rb_ctx* ctx, const void* q, rb_kv_cache* c, int3
   for (int b = 0; b < batch; ++b)
     RB_REQUIRE(c->host_lens[b] >= s_new, "rb_attention: sequence %d holds %d tokens, fewer than the %d new ones", b,
                c->host_lens[b], s_new);
+  double kv_tokens = 0.0, pairs = 0.0;  // keys read; (query, key) pairs under the causal mask
+  for (int b = 0; b < batch; ++b) {
+    const double len = c->host_lens[b];
+    kv_tokens += len;
+    pairs += (double)s_new * (len - s_new) + 0.5 * s_new * (s_new + 1.0);
+  }
+  const double es = (double)dtype_size(dtype), d = c->head_dim;
+  ProfScope prof(ctx, RB_PROF_ATTENTION,
+                 es * (2.0 * kv_tokens * c->kv_heads * d + 2.0 * batch * s_new * q_heads * d), 4.0 * pairs * q_heads * d);
   if (dtype == RB_BF16 && !ctx->debug_simple) return attention_mma_bf16(ctx, q, c, layer, batch, s_new, q_heads, scale, out);
   return attention_simple(ctx, q, c, layer, batch, s_new, q_heads, scale, out, dtype);
 }

@@ -19,6 +19,10 @@ struct rb_ctx {
   // Tensor maps are keyed by (base pointer, rows, cols, row stride in elements, box rows).
   std::map<std::tuple<const void*, int64_t, int64_t, int64_t, int>, CUtensorMap> tmaps;
   bool debug_simple = false;  // RAI_B200_SIMPLE=1: route bf16 through the plain kernels (debugging aid)
+  // Optional per-launch timing (rb_profile_start / rb_profile_read): an event pair around each launch.
+  struct ProfRec { int cls; cudaEvent_t a, b; double bytes, flops; };
+  bool profiling = false;
+  std::vector<ProfRec> prof;
 };
 
 // Pages of 64 tokens.  K and V each: [layer][page][kv_head][64][head_dim] in the cache dtype.
@@ -36,6 +40,25 @@ struct rb_kv_cache {
 
 namespace rb {
 constexpr int kPageTokens = 64;
+
+// Brackets one kernel launch with CUDA events when profiling is on; `bytes` / `flops` are the
+// algorithmic (not measured) HBM bytes and floating-point operations of the launch.
+struct ProfScope {
+  rb_ctx* ctx;
+  size_t idx = 0;
+  bool on;
+  ProfScope(rb_ctx* c, int cls, double bytes, double flops) : ctx(c), on(c->profiling) {
+    if (!on) return;
+    rb_ctx::ProfRec r{cls, nullptr, nullptr, bytes, flops};
+    if (cudaEventCreate(&r.a) != cudaSuccess || cudaEventCreate(&r.b) != cudaSuccess) { on = false; return; }
+    cudaEventRecord(r.a, c->stream);
+    idx = c->prof.size();
+    c->prof.push_back(r);
+  }
+  ~ProfScope() {
+    if (on) cudaEventRecord(ctx->prof[idx].b, ctx->stream);
+  }
+};
 
 // Internal launchers shared between api.cu and model.cu (defined next to their kernels).
 int tmap_2d_bf16(rb_ctx* ctx, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows,

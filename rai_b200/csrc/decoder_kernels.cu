@@ -192,6 +192,7 @@ extern "C" int32_t rb_embed_gather(rb_ctx* ctx, const void* table, int32_t dtype
   RB_REQUIRE(ctx && table && ids && out, "rb_embed_gather: null argument");
   RB_REQUIRE(vocab > 0 && hidden > 0 && n_ids >= 0, "rb_embed_gather: bad sizes");
   if (n_ids == 0) return RB_OK;
+  ProfScope prof(ctx, RB_PROF_EMBED, 2.0 * n_ids * hidden * dtype_size(dtype), 0.0);
   const int threads = 128;
   if (dtype == RB_BF16)
     embed_gather_kernel<__nv_bfloat16><<<(unsigned)n_ids, threads, 0, ctx->stream>>>(
@@ -220,6 +221,9 @@ extern "C" int32_t rb_norm(rb_ctx* ctx, int32_t kind, const void* x, const void*
   const size_t smem = (size_t)hidden * sizeof(float);
   const int threads = hidden >= 2048 ? 512 : 256;
   const size_t acc_stride = (size_t)rows * hidden;
+  ProfScope prof(ctx, RB_PROF_NORM,
+                 (double)rows * hidden * (dtype_size(dtype) * ((x ? 1 : 0) + (add ? 1 : 0) + (out ? 1 : 0) + (sum_out ? 1 : 0)) + 4.0 * n_acc),
+                 0.0);
   if (dtype == RB_BF16) {
     auto kern = norm_kernel<__nv_bfloat16>;
     if (smem > 48 * 1024) RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -284,6 +288,7 @@ extern "C" int32_t rb_rope_kv_append(rb_ctx* ctx, const void* qkv, const float* 
   const size_t acc_stride = (size_t)batch * s_new * ncol;
   const size_t loff = (size_t)layer * c->layer_stride_elems();
   const int threads = 256;
+  ProfScope prof(ctx, RB_PROF_ROPE_KV, (double)batch * s_new * ncol * (dtype_size(dtype) * (qkv ? 2.0 : 1.0) + 4.0 * n_acc), 0.0);
   if (dtype == RB_BF16) {
     auto kern = rope_kv_append_kernel<__nv_bfloat16>;
     if (smem > 48 * 1024) RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -311,6 +316,7 @@ extern "C" int32_t rb_argmax_rows(rb_ctx* ctx, const void* logits, int32_t dtype
   RB_REQUIRE(ctx && logits && out, "rb_argmax_rows: null argument");
   RB_REQUIRE(rows >= 0 && cols > 0 && cols <= 0xffffffffLL, "rb_argmax_rows: bad sizes");
   if (rows == 0) return RB_OK;
+  ProfScope prof(ctx, RB_PROF_ARGMAX, (double)rows * cols * dtype_size(dtype), 0.0);
   if (dtype == RB_BF16)
     argmax_rows_kernel<__nv_bfloat16><<<(unsigned)rows, 1024, 0, ctx->stream>>>((const __nv_bfloat16*)logits, cols, out);
   else if (dtype == RB_F32)
