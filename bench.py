@@ -1,0 +1,468 @@
+"""Benchmark of the decoder hot path on B200: batch-64 KV-cached decode (the headline) and 8 x 4096
+prefill of the Qwen2-7B architecture in bf16, tensor-parallel over --gpus ranks.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One "step" is one decode step of the whole batch (64 new tokens at a 2048-token context that grows by
+one per step).  Rank 0 prints ONE JSON line.  Weights are random-init N(0, 0.02) bf16 and token ids
+uniform random (no checkpoints or datasets are available offline); the KV cache is filled by really
+prefilling random prompts.  `--impl reference` times the CPU restatement of rai's own Cpu path
+(oracle/rai_cpu.py; rai itself cannot be built here) on the host cores, on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+NOMINAL_HBM_GBS = 8000.0        # the roofline basis the benchmark definition names
+NOMINAL_BF16_TFLOPS = 2250.0
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="qwen2-7b")
+    ap.add_argument("--decode-batch", type=int, default=64)
+    ap.add_argument("--context", type=int, default=2048)
+    ap.add_argument("--prefill-batch", type=int, default=8)
+    ap.add_argument("--prefill-len", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only)")
+    ap.add_argument("--skip-prefill", action="store_true")
+    ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--profile-steps", type=int, default=8)
+    ap.add_argument("--skip-fill", action="store_true",
+                    help="leave the KV cache zero-filled instead of prefilling it (same traffic; for profiler runs)")
+    return ap.parse_args()
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"]))}, "measured"
+    except Exception:
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while a timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
+
+    def mark(self):
+        return time.perf_counter()
+
+    def stop(self):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()   # our own child, by handle
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+
+    def summary(self, t_begin=None, t_end=None):
+        """Median SM clock and the throttle reasons seen between the two marks (all samples if none)."""
+        sm, mx, reasons = [], 0.0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = [r for t, r in self.rows if (t_begin is None or t >= t_begin) and (t_end is None or t <= t_end + 0.12)]
+        if not rows:
+            rows = [r for _, r in self.rows[-3:]]
+        for r in rows:
+            try:
+                sm.append(float(r[0]))
+                mx = max(mx, float(r[1]))
+                for n, v in zip(names, r[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except Exception:
+                continue
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def decode_step_bytes(cfg, param_bytes_no_embed, batch, ctx):
+    """Algorithmic HBM bytes of one decode step: every streamed parameter once, `batch` embedding
+    rows, the K and V of `ctx` cached tokens per sequence, and the new token's K and V."""
+    from rai_b200 import configs
+    L, d = cfg["num_hidden_layers"], configs.head_dim(cfg)
+    nkv = cfg.get("num_key_value_heads") or cfg["num_attention_heads"]
+    kv_token = 2 * L * nkv * d * 2
+    return param_bytes_no_embed + batch * cfg["hidden_size"] * 2 + batch * ctx * kv_token + batch * kv_token
+
+
+def prefill_flops(cfg, batch, seq):
+    """2*params*tokens for the linears, last-position lm_head, causal attention (QK^T and PV)."""
+    from rai_b200 import configs
+    H, I, L, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"], cfg["vocab_size"]
+    nq, d = cfg["num_attention_heads"], configs.head_dim(cfg)
+    nkv = cfg.get("num_key_value_heads") or nq
+    per_layer = H * (nq + 2 * nkv) * d + nq * d * H + 3 * H * I
+    linear = 2.0 * per_layer * L * batch * seq + 2.0 * H * V * batch
+    attn = L * batch * 2.0 * nq * seq * seq * d  # = 4 * nq * d * seq^2 / 2
+    return linear, attn
+
+
+# --------------------------------------------------------------------------------------------------
+# CPU arm: the oracle on the host cores, bounded sample
+# --------------------------------------------------------------------------------------------------
+def cpu_decode_sample(cfg, batch, ctx, steps, warmup):
+    """Times the CPU restatement on a bounded sample of the same workload: the full-width model with
+    1 and 2 layers, batch `batch`, a `ctx`-token cache injected as random K/V, `steps` decode steps
+    each.  Per-layer and outside-the-layers times are separated by the difference and extrapolated
+    to the full depth."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import torch
+    import adapter
+    import rai_cpu
+    from rai_b200 import configs, synth
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(1234)
+    full_layers = cfg["num_hidden_layers"]
+    cfg2 = dict(cfg, num_hidden_layers=2, max_position_embeddings=ctx + steps + warmup + 8)
+    params = {}
+    for name, shape, kind in synth.param_shapes(cfg2):
+        if kind == "norm_w":
+            params[name] = torch.ones(shape)
+        else:
+            params[name] = torch.randn(shape, generator=g) * 0.02
+    nkv = cfg.get("num_key_value_heads") or cfg["num_attention_heads"]
+    d = configs.head_dim(cfg)
+    times = {}
+    for n_layers in (1, 2):
+        c = dict(cfg2, num_hidden_layers=n_layers)
+        model = rai_cpu.build(adapter.oracle_config(c), adapter.oracle_params(c, params))
+        model.kv = [(torch.randn(batch, nkv, ctx, d, generator=g), torch.randn(batch, nkv, ctx, d, generator=g))
+                    for _ in range(n_layers)]
+        ids = torch.randint(0, cfg["vocab_size"], (batch, 1), generator=g)
+        ts = []
+        for i in range(warmup + steps):
+            t0 = time.perf_counter()
+            logits = model.forward(ids, ctx + i)
+            ids = logits.reshape(batch, -1).argmax(-1, keepdim=True)
+            if i >= warmup:
+                ts.append(time.perf_counter() - t0)
+        times[n_layers] = statistics.median(ts)
+        del model
+    per_layer = max(times[2] - times[1], 1e-9)
+    outside = max(times[1] - per_layer, 0.0)
+    step_s = outside + full_layers * per_layer
+    return {"value": batch / step_s, "unit": "tok/s", "cores": cores, "kind": "port",
+            "sample": (f"torch-CPU float32 restatement of rai's Cpu path, full-width {cfg['arch']} layers: 1- and 2-layer "
+                       f"models, batch {batch}, {ctx}-token cache injected, {steps} decode steps each (median); "
+                       f"per-layer {per_layer * 1e3:.0f} ms, outside layers {outside * 1e3:.0f} ms, extrapolated to "
+                       f"{full_layers} layers = {step_s:.2f} s/step"),
+            "ms_per_step": step_s * 1e3}
+
+
+def run_reference(args):
+    from rai_b200 import configs
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = configs.get(args.config)
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    steps, warmup = max(1, min(args.steps, 3)), max(1, min(args.warmup, 1))
+    t0 = time.perf_counter()
+    base = cpu_decode_sample(cfg, args.decode_batch, args.context, steps, warmup)
+    line = {
+        "impl": "reference", "metric": "decode_tokens_per_s", "value": base["value"], "unit": "tok/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, cfg, args.gpus),
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "wall_s": time.perf_counter() - t0,
+        "note": ("rai's Cpu (candle) path cannot be built in this environment (no Rust toolchain); this is its "
+                 f"op-for-op restatement timed on {base['cores']} host threads, {steps} sample step(s) per model"),
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, cfg, n):
+    return {"workload": (f"{args.config} architecture, bf16, batch-{args.decode_batch} greedy decode with KV cache at a "
+                         f"{args.context}-token context (+1 per step); prefill {args.prefill_batch} x {args.prefill_len}"),
+            "layers": cfg["num_hidden_layers"], "decode_batch": args.decode_batch, "context": args.context,
+            "prefill_batch": args.prefill_batch, "prefill_len": args.prefill_len,
+            "parallelism": f"tp{n}", "l2": "inputs larger than L2 (>= 14 GB of weights and KV streamed per step)"}
+
+
+# --------------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    from rai_b200 import _lib, configs, synth
+    from rai_b200.device import Cuda
+    from rai_b200.models import Model
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if dist is None:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    cfg = configs.get(args.config)
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    B, T0, K, W = args.decode_batch, args.context, args.steps, args.warmup
+    PB, PS = args.prefill_batch, args.prefill_len
+    chunk = 256
+    max_seq = max(T0 + K + W + 64, 0 if args.skip_prefill else PS)
+    cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], max_seq)
+    max_tokens = max(B * chunk, 0 if args.skip_prefill else PB * PS)
+    dev = Cuda(local)
+    model = Model(cfg, _lib.BF16, dev, max(B, PB), max_seq, max_tokens, tp_rank=rank, tp_size=world)
+    if world > 1:
+        uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            buf = ctypes.create_string_buffer(128)
+            _lib.call("rb_tp_unique_id", buf)
+            uid = torch.tensor(list(buf.raw), dtype=torch.uint8, device="cuda")
+        dist.broadcast(uid, 0)
+        model.tp_init(bytes(uid.cpu().tolist()))
+
+    # ---- random-init weights, generated on the device (identical on every rank; the library shards)
+    gen = torch.Generator(device="cuda").manual_seed(1234)
+    for name, shape, kind in synth.param_shapes(cfg):
+        if kind == "norm_w":
+            w = torch.ones(shape, device="cuda", dtype=torch.bfloat16)
+        else:
+            w = (torch.randn(shape, generator=gen, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        model.update_param(name, w)
+        del w
+    model.finalize()
+    torch.cuda.empty_cache()
+    cache = ctypes.c_void_p(_lib.lib().rb_model_kv_cache(model._m))
+    tok_gen = torch.Generator(device="cuda").manual_seed(99)
+
+    def rewind(n_tokens):
+        _lib.call("rb_kv_cache_set_len", cache, B, n_tokens)
+
+    # ---- fill the cache to the decode context by really prefilling random prompts, chunk by chunk
+    model.clear_kv_cache()
+    logits_buf = torch.empty((max(B, PB), cfg["vocab_size"]), dtype=torch.bfloat16, device="cuda")
+    for pos in range(0, 0 if args.skip_fill else T0, chunk):
+        n = min(chunk, T0 - pos)
+        ids = torch.randint(0, cfg["vocab_size"], (B, n), generator=tok_gen, device="cuda", dtype=torch.int32)
+        _lib.call("rb_model_forward", model._m, ctypes.c_void_p(ids.data_ptr()), B, n, pos,
+                  ctypes.c_void_p(logits_buf.data_ptr()))
+    dev.synchronize()
+    if args.skip_fill:
+        rewind(T0)
+        logits_buf.zero_()
+    first = logits_buf[:B].float().argmax(-1).to(torch.int32).contiguous()
+
+    # ---- decode: W warm-up steps, rewind, then exactly K timed steps on the device
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    if W > 0:
+        model.decode_loop(first, T0, W)
+        dev.synchronize()
+    rewind(T0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    launches0 = dev.launch_count()
+    t_begin = sampler.mark()
+    torch.cuda.nvtx.range_push("decode_timed")
+    e0.record()
+    out_tokens = model.decode_loop(first, T0, K)
+    e1.record()
+    barrier()
+    dev.synchronize()
+    torch.cuda.nvtx.range_pop()
+    t_end = sampler.mark()
+    decode_ms = max_over_ranks(e0.elapsed_time(e1))
+    launches = dev.launch_count() - launches0
+    if rank == 0:
+        sampler.stop()
+    clocks = sampler.summary(t_begin, t_end) if rank == 0 else None
+    decode_tok_s = B * K / (decode_ms / 1e3)
+
+    # ---- per-kernel-class timing of the same steps (event pair around every launch; separate pass)
+    classes = ["gemm", "attention", "norm", "rope_kv", "embed", "argmax", "other"]
+    prof = {}
+    PK = max(1, min(args.profile_steps, K))
+    rewind(T0)
+    _lib.call("rb_profile_start", dev.ctx)
+    model.decode_loop(first, T0, PK)
+    for i, cname in enumerate(classes):
+        out4 = (ctypes.c_double * 4)()
+        _lib.call("rb_profile_read", dev.ctx, i, out4)
+        if out4[0] > 0:
+            prof[cname] = {"launches_per_step": out4[0] / PK, "ms_per_step": out4[1] / PK,
+                           "gbytes_per_step": out4[2] / PK / 1e9, "avg_launch_us": out4[1] / out4[0] * 1e3,
+                           "achieved_gbs": out4[2] / 1e9 / (out4[1] / 1e3) if out4[1] > 0 else None}
+    dev.synchronize()
+
+    # ---- end to end through the generation-step call: pinned host tokens in, token ids out, per step
+    e2e = None
+    if not args.skip_e2e:
+        rewind(T0)
+        tin = first.cpu().reshape(B, 1).pin_memory()
+        tout = torch.empty(B, dtype=torch.int32).pin_memory()
+        for i in range(min(W, 3)):
+            model.generate_step(tin, T0 + i, tout)
+            tin.copy_(tout.reshape(B, 1))
+        rewind(T0)
+        tin.copy_(first.cpu().reshape(B, 1))
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(K):
+            model.generate_step(tin, T0 + i, tout)
+            tin.copy_(tout.reshape(B, 1))
+        barrier()
+        e2e_s = max_over_ranks(time.perf_counter() - t0)
+        e2e = {"value": B * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": B * 4, "d2h_bytes_per_step": B * 4,
+               "ms_per_step": e2e_s / K * 1e3,
+               "api": "rb_model_generate_step: pinned host token ids -> H2D -> forward -> on-device argmax -> D2H"}
+
+    # ---- prefill: PB x PS tokens from an empty cache
+    prefill = None
+    if not args.skip_prefill:
+        ids = torch.randint(0, cfg["vocab_size"], (PB, PS), generator=tok_gen, device="cuda", dtype=torch.int32)
+
+        def one_prefill():
+            model.clear_kv_cache()
+            _lib.call("rb_model_forward", model._m, ctypes.c_void_p(ids.data_ptr()), PB, PS, 0,
+                      ctypes.c_void_p(logits_buf.data_ptr()))
+        one_prefill()
+        dev.synchronize()
+        reps = 3
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        psampler = ClockSampler(local)
+        if rank == 0:
+            psampler.start()
+        barrier()
+        pt0 = psampler.mark()
+        torch.cuda.nvtx.range_push("prefill_timed")
+        p0.record()
+        for _ in range(reps):
+            one_prefill()
+        p1.record()
+        barrier()
+        dev.synchronize()
+        torch.cuda.nvtx.range_pop()
+        pt1 = psampler.mark()
+        if rank == 0:
+            psampler.stop()
+        pms = max_over_ranks(p0.elapsed_time(p1)) / reps
+        lin, att = prefill_flops(cfg, PB, PS)
+        prefill = {"tokens_per_s": PB * PS / (pms / 1e3), "ms_per_pass": pms, "tflops": (lin + att) / 1e12 / (pms / 1e3),
+                   "flops_linear": lin, "flops_attention_causal": att, "passes": reps,
+                   "clocks": psampler.summary(pt0, pt1) if rank == 0 else None}
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_kind = measured_peaks()
+    # whole-model parameter bytes streamed per step: everything but the embedding table (of which only
+    # `batch` rows are read), unless the table doubles as lm_head
+    param_no_embed = sum(2 * int(__import__("math").prod(shape)) for name, shape, _ in synth.param_shapes(cfg)
+                         if name != "model.embed_tokens.weight" or configs.tied(cfg))
+    bytes_first = decode_step_bytes(cfg, param_no_embed, B, T0)
+    bytes_last = decode_step_bytes(cfg, param_no_embed, B, T0 + K - 1)
+    step_bytes = 0.5 * (bytes_first + bytes_last)
+    step_gbs = step_bytes / 1e9 / (decode_ms / K / 1e3)
+    gemm = prof.get("gemm", {})
+    roofline = {
+        "bound": "hbm", "kernel": "gemm_tc_kernel (weight-streaming tcgen05 GEMM; all Linear layers of a decode step)",
+        "achieved": gemm.get("achieved_gbs"), "peak": peaks["hbm_gbs"] * world, "unit": "GB/s",
+        "frac": (gemm["achieved_gbs"] / (peaks["hbm_gbs"] * world)) if gemm.get("achieved_gbs") else None,
+        "peak_kind": f"{peak_kind} stream-copy bandwidth x {world} GPU(s)",
+        "traffic": None,
+        "avg_launch_us": gemm.get("avg_launch_us"), "launches_per_step": gemm.get("launches_per_step"),
+        "algorithmic_gbytes_per_step": gemm.get("gbytes_per_step"),
+        "whole_step": {"algorithmic_gbytes": step_bytes / 1e9, "achieved_gbs": step_gbs,
+                       "frac_of_measured_copy": step_gbs / (peaks["hbm_gbs"] * world),
+                       "frac_of_nominal_8tbs": step_gbs / (NOMINAL_HBM_GBS * world)},
+        "per_class": prof,
+    }
+    if prefill:
+        prefill["frac_of_measured_sustained_bf16"] = prefill["tflops"] / (peaks["bf16_tflops_sustained"] * world)
+        prefill["frac_of_nominal_bf16"] = prefill["tflops"] / (NOMINAL_BF16_TFLOPS * world)
+    cpu = None
+    if world == 1 and not args.skip_cpu:
+        base = cpu_decode_sample(cfg, B, T0, 2, 1)
+        cpu = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    line = {
+        "metric": "decode_tokens_per_s", "value": decode_tok_s, "unit": "tok/s", "n_gpus": world, "steps": K,
+        "warmup": W, "ms_per_step": decode_ms / K, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args, cfg, world), "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
+        "roofline": roofline, "cpu_baseline": cpu, "prefill": prefill,
+        "tokens_checksum": int(out_tokens.to(torch.int64).sum().item()),
+    }
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

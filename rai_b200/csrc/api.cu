@@ -34,6 +34,11 @@ int fail(int code, const char* fmt, ...) {
 
 using namespace rb;
 
+static void prof_clear(rb_ctx* ctx) {
+  for (auto& r : ctx->prof) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+  ctx->prof.clear();
+}
+
 extern "C" const char* rb_last_error(void) { return g_last_error.c_str(); }
 
 extern "C" int32_t rb_init(int32_t device, rb_ctx** out) {
@@ -97,11 +102,6 @@ extern "C" int32_t rb_sync(rb_ctx* ctx) {
     return fail(code, "device-side check failed: code %d at 0x%x (detail %u, %u)", code, w[1], w[2], w[3]);
   }
   return RB_OK;
-}
-
-static void prof_clear(rb_ctx* ctx) {
-  for (auto& r : ctx->prof) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
-  ctx->prof.clear();
 }
 
 extern "C" int32_t rb_profile_start(rb_ctx* ctx) {
