@@ -382,13 +382,13 @@ def run_ours(args):
             model.clear_kv_cache()
             _lib.call("rb_model_forward", model._m, ctypes.c_void_p(ids.data_ptr()), PB, PS, 0,
                       ctypes.c_void_p(logits_buf.data_ptr()))
+        psampler = ClockSampler(local)
+        if rank == 0:
+            psampler.start()
         one_prefill()
         dev.synchronize()
         reps = 3
         p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        psampler = ClockSampler(local)
-        if rank == 0:
-            psampler.start()
         barrier()
         pt0 = psampler.mark()
         torch.cuda.nvtx.range_push("prefill_timed")

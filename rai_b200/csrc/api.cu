@@ -62,8 +62,14 @@ extern "C" int32_t rb_init(int32_t device, rb_ctx** out) {
   c->stream = c->own_stream;
   RB_CUDA(cudaMalloc(&c->status_dev, 4 * sizeof(uint32_t)));
   RB_CUDA(cudaMemset(c->status_dev, 0, 4 * sizeof(uint32_t)));
+  RB_CUDA(cudaMalloc(&c->argmax_best, kArgmaxRows * sizeof(unsigned long long)));
+  RB_CUDA(cudaMalloc(&c->argmax_count, kArgmaxRows * sizeof(unsigned int)));
+  RB_CUDA(cudaMemset(c->argmax_best, 0, kArgmaxRows * sizeof(unsigned long long)));
+  RB_CUDA(cudaMemset(c->argmax_count, 0, kArgmaxRows * sizeof(unsigned int)));
   const char* dbg = getenv("RAI_B200_SIMPLE");
   c->debug_simple = dbg && dbg[0] == '1';
+  const char* pdl = getenv("RAI_B200_PDL");
+  c->pdl = !(pdl && pdl[0] == '0');
   *out = c;
   return RB_OK;
 }
@@ -74,6 +80,8 @@ extern "C" int32_t rb_destroy(rb_ctx* ctx) {
   cudaStreamSynchronize(ctx->stream);
   prof_clear(ctx);
   if (ctx->status_dev) cudaFree(ctx->status_dev);
+  if (ctx->argmax_best) cudaFree(ctx->argmax_best);
+  if (ctx->argmax_count) cudaFree(ctx->argmax_count);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
   delete ctx;
   return RB_OK;

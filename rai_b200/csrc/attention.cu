@@ -13,6 +13,8 @@
 //            merge their (max, sum, O) at the end.  With more than one split a small kernel merges
 //            the per-split partials.
 // HBM-bound at decode: algorithmic bytes = 2 * len * kv_heads * head_dim * 2 per sequence and layer.
+#include <stdlib.h>
+
 #include <algorithm>
 
 #include "ctx.h"
@@ -91,6 +93,8 @@ __global__ void __launch_bounds__(128, (D <= 128) ? 2 : 1) attention_kernel(cons
   uint8_t* kv_s = smem + C::kQBytes;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
+  pdl_launch_dependents();
+  pdl_wait();  // q and the newest K/V rows come from the kernel before this one
 
   int b, head, kvh, q0 = 0, split = 0;
   if (DECODE) {
@@ -319,6 +323,8 @@ __global__ void __launch_bounds__(128, (D <= 128) ? 2 : 1) attention_kernel(cons
 // Merges the per-split (max, sum, O) of the decode kernel: one block per (sequence, head).
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        int n_splits, int d, bf16* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t bh = blockIdx.x;
   float M = -INFINITY;
   for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(bh * n_splits + s) * 2]);
@@ -351,21 +357,26 @@ int launch_attention(rb_ctx* ctx, AParams& p, int batch, int max_len) {
     if (!set) { RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes)); set = true; }
     dim3 grid((unsigned)((p.s_new + 63) / 64), (unsigned)p.q_heads, (unsigned)batch);
     p.n_splits = 1;
-    kern<<<grid, 128, C::kSmemBytes, ctx->stream>>>(p);
+    RB_CUDA(launch_kernel(kern, grid, dim3(128), (size_t)C::kSmemBytes, ctx->stream, ctx->pdl, p));
     ctx->launches++;
-    return launch_status("attention_prefill");
+    return RB_OK;
   }
   using C = ACfg<D, true>;
   auto kern = attention_kernel<D, true>;
   static bool set = false;
   if (!set) { RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes)); set = true; }
+  // Split the keys of a sequence over several blocks only when (sequence, KV head) pairs alone leave
+  // the GPU under-filled: one long block per pair keeps its copy pipeline full and needs no merge.
   const int tiles = std::max(1, (max_len + kTile - 1) / kTile);
   const int work = batch * p.kv_heads;
-  int splits = (2 * ctx->sm_count + work - 1) / work;
-  splits = std::max(1, std::min(splits, std::min(tiles, 32)));
-  if (splits > 1) {  // no split may be shorter than 2 tiles: the merge costs more than it saves
-    splits = std::max(1, std::min(splits, tiles / 2));
+  const int slots = 2 * ctx->sm_count;
+  int splits = 1;
+  if (work * 4 < slots * 3) {
+    splits = (slots + work - 1) / work;
+    splits = std::max(1, std::min(splits, std::min(tiles / 2, 32)));  // at least 2 tiles per split
   }
+  static const int forced = getenv("RAI_B200_ATTN_SPLITS") ? atoi(getenv("RAI_B200_ATTN_SPLITS")) : 0;
+  if (forced > 0) splits = std::max(1, std::min(forced, tiles));
   p.n_splits = splits;
   if (splits > 1) {
     const size_t need = (size_t)batch * p.q_heads * splits * (D + 2) * sizeof(float);
@@ -380,13 +391,12 @@ int launch_attention(rb_ctx* ctx, AParams& p, int batch, int max_len) {
     p.part_ml = sc.ptr + (size_t)batch * p.q_heads * splits * D;
   }
   dim3 grid((unsigned)splits, (unsigned)p.kv_heads, (unsigned)batch);
-  kern<<<grid, 128, C::kSmemBytes, ctx->stream>>>(p);
+  RB_CUDA(launch_kernel(kern, grid, dim3(128), (size_t)C::kSmemBytes, ctx->stream, ctx->pdl, p));
   ctx->launches++;
-  RB_TRY(launch_status("attention_decode"));
   if (splits > 1) {
-    attention_merge_kernel<<<batch * p.q_heads, 128, 0, ctx->stream>>>(p.part_o, p.part_ml, splits, D, p.out);
+    RB_CUDA(launch_kernel(attention_merge_kernel, dim3((unsigned)(batch * p.q_heads)), dim3(128), 0, ctx->stream, ctx->pdl,
+                          (const float*)p.part_o, (const float*)p.part_ml, splits, D, p.out));
     ctx->launches++;
-    RB_TRY(launch_status("attention_merge"));
   }
   return RB_OK;
 }

@@ -6,6 +6,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <string>
+#include <utility>
 
 #include "../../include/rai_b200.h"
 
@@ -48,6 +49,31 @@ inline size_t dtype_size(int dt) {
     case RB_I64: case RB_F64: return 8;
   }
   return 0;
+}
+
+// Programmatic dependent launch.  Kernels of the decoder chain are launched with the
+// programmatic-stream-serialization attribute: a kernel may become resident while its predecessor
+// is still running, does whatever does not depend on the predecessor (barrier set-up, TMEM
+// allocation, prefetch of weights), and calls pdl_wait() before it touches anything the
+// predecessor produced or may still be reading.  pdl_launch_dependents() lets the successor do the same.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Launches `kern` with the programmatic-stream-serialization attribute when `pdl` is set.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 bool pdl, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(std::forward<Args>(args))...);
 }
 
 // Device status word: kernels that wait on barriers record a give-up here instead of trapping.

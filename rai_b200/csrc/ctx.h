@@ -18,6 +18,10 @@ struct rb_ctx {
   int64_t launches = 0;
   // Tensor maps are keyed by (base pointer, rows, cols, row stride in elements, box rows).
   std::map<std::tuple<const void*, int64_t, int64_t, int64_t, int>, CUtensorMap> tmaps;
+  bool pdl = true;            // RAI_B200_PDL=0 turns programmatic dependent launch off (debugging aid)
+  // argmax across blocks: running best (key << 32 | index) and arrival count per row; self-resetting
+  unsigned long long* argmax_best = nullptr;
+  unsigned int* argmax_count = nullptr;
   bool debug_simple = false;  // RAI_B200_SIMPLE=1: route bf16 through the plain kernels (debugging aid)
   // Optional per-launch timing (rb_profile_start / rb_profile_read): an event pair around each launch.
   struct ProfRec { int cls; cudaEvent_t a, b; double bytes, flops; };
@@ -40,6 +44,7 @@ struct rb_kv_cache {
 
 namespace rb {
 constexpr int kPageTokens = 64;
+constexpr int kArgmaxRows = 4096;  // rows one argmax launch can reduce across blocks
 
 // Brackets one kernel launch with CUDA events when profiling is on; `bytes` / `flops` are the
 // algorithmic (not measured) HBM bytes and floating-point operations of the launch.

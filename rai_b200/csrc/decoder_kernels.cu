@@ -3,6 +3,7 @@
 // data with float32 arithmetic inside, whatever the storage dtype.
 #include <math.h>
 
+#include <algorithm>
 #include <vector>
 
 #include "ctx.h"
@@ -16,6 +17,8 @@ namespace rb {
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const uint32_t* __restrict__ ids, int64_t vocab,
                                     int hidden, float scale, T* __restrict__ out, uint32_t* status) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t i = blockIdx.x;
   uint32_t id = ids[i];
   if (id >= (uint64_t)vocab) {  // record and clamp: never read out of bounds, never trap
@@ -51,6 +54,8 @@ __global__ void norm_kernel(int kind, const T* __restrict__ x, const T* __restri
                             float eps, int hidden, T* __restrict__ out, T* __restrict__ sum_out) {
   extern __shared__ float row_f[];
   __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t base = (size_t)blockIdx.x * hidden;
   float s = 0.f;
   const float inv_sqrt_h = 1.0f / sqrtf((float)hidden);
@@ -92,6 +97,124 @@ __global__ void norm_kernel(int kind, const T* __restrict__ x, const T* __restri
   }
 }
 
+
+// 8 elements per thread-chunk, at most kChunks chunks per thread held in registers: every load of
+// the row (inputs, residual, all split-K slabs, bias) is in flight at once, which is what matters at
+// decode where only `rows` blocks exist and the kernel is pure latency.
+__device__ __forceinline__ void load8(const float* p, float* v) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* v) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void store8(float* p, const float* v) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float* v) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+template <typename T>
+__device__ __forceinline__ void round_to(float* v) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = Cvt<T>::to_f(Cvt<T>::from_f(v[i]));
+}
+
+template <typename T, int kChunks>
+__global__ void norm_vec_kernel(int kind, const T* __restrict__ x, const T* __restrict__ add,
+                                const float* __restrict__ acc, int n_acc, size_t acc_stride,
+                                const T* __restrict__ acc_bias, const T* __restrict__ w, const T* __restrict__ b,
+                                float eps, int hidden, T* __restrict__ out, T* __restrict__ sum_out) {
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  float wv[kChunks][8], bv[kChunks][8];
+  const int nchunk = hidden >> 3;
+  // weights do not depend on the previous kernel: fetch them before waiting for it
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { wv[c][i] = 1.f; bv[c][i] = 0.f; }
+    if (ch < nchunk && out) {
+      if (w) load8(w + ch * 8, wv[c]);
+      if (b) load8(b + ch * 8, bv[c]);
+    }
+  }
+  pdl_wait();
+  const size_t base = (size_t)blockIdx.x * hidden;
+  float v[kChunks][8];
+  float s = 0.f;
+  const float inv_sqrt_h = 1.0f / sqrtf((float)hidden);
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[c][i] = 0.f;
+    if (ch >= nchunk) continue;
+    float t[8];
+    if (x) { load8(x + base + ch * 8, t);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[c][i] += t[i]; }
+    if (add) { load8(add + base + ch * 8, t);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[c][i] += t[i]; }
+    for (int k = 0; k < n_acc; ++k) { load8(acc + (size_t)k * acc_stride + base + ch * 8, t);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[c][i] += t[i]; }
+    if (acc_bias) { load8(acc_bias + ch * 8, t);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[c][i] += t[i]; }
+    round_to<T>(v[c]);  // the residual stream is stored in the model dtype
+    if (sum_out) store8(sum_out + base + ch * 8, v[c]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (kind == RB_NORM_LAYER) s += v[c][i];
+      else if (kind == RB_NORM_RMS) { const float t2 = v[c][i] * inv_sqrt_h; s += t2 * t2; }
+      else s += v[c][i] * v[c][i];
+    }
+  }
+  if (!out) return;
+  s = block_sum(s, red);
+  float mean = 0.f, r;
+  if (kind == RB_NORM_LAYER) {
+    mean = s / (float)hidden;
+    float q = 0.f;
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c)
+      if (threadIdx.x + c * blockDim.x < nchunk) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { const float d = v[c][i] - mean; q += d * d; }
+      }
+    q = block_sum(q, red);
+    r = 1.0f / sqrtf(q / (float)hidden + eps);
+  } else if (kind == RB_NORM_RMS) {
+    r = 1.0f / sqrtf(s + eps);
+  } else {
+    r = 1.0f / sqrtf(s / (float)hidden + eps);
+  }
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch >= nchunk) continue;
+    float y[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (kind == RB_NORM_LAYER) { y[i] = (v[c][i] - mean) * r; if (w) y[i] = wv[c][i] * y[i] + bv[c][i]; }
+      else if (kind == RB_NORM_RMS) y[i] = wv[c][i] * v[c][i] * r;
+      else y[i] = v[c][i] * r * (wv[c][i] + 1.0f);
+    }
+    store8(out + base + ch * 8, y);
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // Head split + RoPE + paged KV append.  One block per token.  Pairing is (i, i + rot/2) within the
 // first `rot` lanes of each head ("rotate_half", qwen2.rs:33-38); lanes >= rot pass through
@@ -106,6 +229,8 @@ __global__ void rope_kv_append_kernel(const T* __restrict__ qkv, const float* __
                                       const int32_t* __restrict__ block_table, const int32_t* __restrict__ seq_lens,
                                       int pages_per_seq, int max_seq, uint32_t* status) {
   extern __shared__ float vals[];  // all (q + 2 kv) * d columns of this token
+  pdl_launch_dependents();
+  pdl_wait();
   const int m = blockIdx.x;
   const int b = m / s_new, s = m % s_new;
   const int ncol = (q_heads + 2 * kv_heads) * d;
@@ -146,6 +271,95 @@ __global__ void rope_kv_append_kernel(const T* __restrict__ qkv, const float* __
   }
 }
 
+
+// Vector form of the kernel above for head_dim % 8 == 0 and (rot/2) % 8 == 0: a work item is
+// either a pair of 8-element chunks (lanes i..i+8 and i+rot/2..) of a q or k head, rotated together,
+// or one pass-through chunk (lanes >= rot, and all of v).  16-byte loads and stores throughout.
+template <typename T>
+__global__ void rope_kv_append_vec_kernel(const T* __restrict__ qkv, const float* __restrict__ acc, int n_acc,
+                                          size_t acc_stride, const T* __restrict__ bias,
+                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot,
+                                          int s_new, int q_heads, int kv_heads, int d, T* __restrict__ q_out,
+                                          T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                          const int32_t* __restrict__ block_table,
+                                          const int32_t* __restrict__ seq_lens, int pages_per_seq, int max_seq,
+                                          uint32_t* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int m = blockIdx.x;
+  const int b = m / s_new, sq = m % s_new;
+  const int ncol = (q_heads + 2 * kv_heads) * d;
+  const int pos = seq_lens[b] - s_new + sq;
+  if (pos < 0 || pos >= max_seq) {
+    if (threadIdx.x == 0) { status[0] = (uint32_t)(-RB_ERR_INVALID); status[1] = 0x20BEu; status[2] = (uint32_t)pos; }
+    return;
+  }
+  const int half = rot >> 1;
+  const int pair_items = half >> 3, pass_items = (d - rot) >> 3;
+  const int per_rot_head = pair_items + pass_items;  // items of one q or k head
+  const int rot_heads = q_heads + kv_heads;
+  const int v_items = d >> 3;
+  const int total = rot_heads * per_rot_head + kv_heads * v_items;
+  const int page = block_table[(size_t)b * pages_per_seq + pos / kPageTokens];
+  const int slot = pos % kPageTokens;
+  const size_t row = (size_t)m * ncol;
+  auto gather = [&](int col, float* v) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    float t[8];
+    if (qkv) { load8(qkv + row + col, t);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] += t[i]; }
+    for (int k = 0; k < n_acc; ++k) { load8(acc + (size_t)k * acc_stride + row + col, t);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] += t[i]; }
+    if (bias) { load8(bias + col, t);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] += t[i]; }
+  };
+  auto emit = [&](int head, int lane0, const float* v) {
+    if (head < q_heads) {
+      store8(q_out + (size_t)m * q_heads * d + head * d + lane0, v);
+    } else {
+      const bool is_v = head >= rot_heads;
+      const int kvh = is_v ? head - rot_heads : head - q_heads;
+      const size_t off = (((size_t)page * kv_heads + kvh) * kPageTokens + slot) * d + lane0;
+      store8((is_v ? v_cache : k_cache) + off, v);
+    }
+  };
+  for (int it = threadIdx.x; it < total; it += blockDim.x) {
+    if (it < rot_heads * per_rot_head) {
+      const int head = it / per_rot_head, j = it % per_rot_head;
+      if (j < pair_items) {
+        const int i0 = j * 8;
+        float lo[8], hi[8], cs[8], sn[8], ylo[8], yhi[8];
+        gather(head * d + i0, lo);
+        gather(head * d + i0 + half, hi);
+        load8(cos_t + (size_t)pos * half + i0, cs);
+        load8(sin_t + (size_t)pos * half + i0, sn);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          ylo[i] = lo[i] * cs[i] - hi[i] * sn[i];  // x*cos + rotate_half(x)*sin, first half: partner is -x[i+half]
+          yhi[i] = hi[i] * cs[i] + lo[i] * sn[i];  // second half: partner is x[i-half]
+        }
+        emit(head, i0, ylo);
+        emit(head, i0 + half, yhi);
+      } else {
+        const int i0 = rot + (j - pair_items) * 8;
+        float v[8];
+        gather(head * d + i0, v);
+        emit(head, i0, v);
+      }
+    } else {
+      const int k = it - rot_heads * per_rot_head;
+      const int head = rot_heads + k / v_items, i0 = (k % v_items) * 8;
+      float v[8];
+      gather(head * d + i0, v);
+      emit(head, i0, v);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // Vocabulary argmax under f32 total order, last index among equals
 // (examples/qwen2/src/main.rs:32-40: `max_by(total_cmp)`).
@@ -155,14 +369,36 @@ __device__ __forceinline__ uint32_t total_order_key(float f) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+// Each row is split over gridDim.x blocks; a block folds its segment into a 64-bit (key << 32 | index)
+// candidate, merges it into the row's running best with atomicMax (order-independent, so the result
+// is deterministic), and the last block to arrive writes the index and resets the scratch words.
 template <typename T>
-__global__ void argmax_rows_kernel(const T* __restrict__ x, int64_t cols, uint32_t* __restrict__ out) {
+__global__ void argmax_rows_kernel(const T* __restrict__ x, int64_t cols, uint32_t* __restrict__ out,
+                                   unsigned long long* __restrict__ best_g, unsigned int* __restrict__ count_g) {
   __shared__ unsigned long long best[32];
-  const T* row = x + (size_t)blockIdx.x * cols;
-  unsigned long long loc = 0;  // (key << 32) | index: larger index wins among equal keys
-  for (int64_t i = threadIdx.x; i < cols; i += blockDim.x) {
-    const unsigned long long cand = ((unsigned long long)total_order_key(Cvt<T>::to_f(row[i])) << 32) | (uint32_t)i;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.y;
+  const T* row = x + (size_t)r * cols;
+  const int64_t seg = ((cols + gridDim.x - 1) / gridDim.x + 7) & ~int64_t(7);
+  const int64_t c0 = (int64_t)blockIdx.x * seg, c1 = min(cols, c0 + seg);
+  unsigned long long loc = 0;
+  auto consider = [&](float f, int64_t i) {
+    const unsigned long long cand = ((unsigned long long)total_order_key(f) << 32) | (uint32_t)i;
     loc = cand > loc ? cand : loc;
+  };
+  const bool vec = ((reinterpret_cast<uintptr_t>(row) & 15) == 0) && ((cols * sizeof(T)) % 16 == 0);
+  if (vec) {
+    for (int64_t i = c0 + (int64_t)threadIdx.x * 8; i + 8 <= c1; i += (int64_t)blockDim.x * 8) {
+      float v[8];
+      load8(row + i, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) consider(v[j], i + j);
+    }
+    const int64_t tail = c0 + ((c1 - c0) & ~int64_t(7));
+    for (int64_t i = tail + threadIdx.x; i < c1; i += blockDim.x) consider(Cvt<T>::to_f(row[i]), i);
+  } else {
+    for (int64_t i = c0 + threadIdx.x; i < c1; i += blockDim.x) consider(Cvt<T>::to_f(row[i]), i);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -179,7 +415,18 @@ __global__ void argmax_rows_kernel(const T* __restrict__ x, int64_t cols, uint32
       const unsigned long long other = __shfl_xor_sync(0xffffffffu, loc, o);
       loc = other > loc ? other : loc;
     }
-    if (lane == 0) out[blockIdx.x] = (uint32_t)(loc & 0xffffffffull);
+    if (lane == 0) {
+      if (gridDim.x == 1) { out[r] = (uint32_t)(loc & 0xffffffffull); return; }
+      atomicMax(&best_g[r], loc);
+      __threadfence();
+      const unsigned int arrived = atomicAdd(&count_g[r], 1u);
+      if (arrived == gridDim.x - 1) {
+        __threadfence();
+        const unsigned long long fin = atomicExch(&best_g[r], 0ull);  // read and reset for the next call
+        count_g[r] = 0u;
+        out[r] = (uint32_t)(fin & 0xffffffffull);
+      }
+    }
   }
 }
 
@@ -187,24 +434,59 @@ __global__ void argmax_rows_kernel(const T* __restrict__ x, int64_t cols, uint32
 
 using namespace rb;
 
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <typename T>
+static int embed_launch(rb_ctx* ctx, const void* table, int64_t vocab, int64_t hidden, const uint32_t* ids, int64_t n_ids,
+                        float scale, void* out) {
+  RB_CUDA(launch_kernel(embed_gather_kernel<T>, dim3((unsigned)n_ids), dim3(128), 0, ctx->stream, ctx->pdl,
+                        (const T*)table, ids, vocab, (int)hidden, scale, (T*)out, ctx->status_dev));
+  return RB_OK;
+}
+
 extern "C" int32_t rb_embed_gather(rb_ctx* ctx, const void* table, int32_t dtype, int64_t vocab, int64_t hidden,
                                    const uint32_t* ids, int64_t n_ids, float scale, void* out) {
   RB_REQUIRE(ctx && table && ids && out, "rb_embed_gather: null argument");
   RB_REQUIRE(vocab > 0 && hidden > 0 && n_ids >= 0, "rb_embed_gather: bad sizes");
   if (n_ids == 0) return RB_OK;
   ProfScope prof(ctx, RB_PROF_EMBED, 2.0 * n_ids * hidden * dtype_size(dtype), 0.0);
-  const int threads = 128;
-  if (dtype == RB_BF16)
-    embed_gather_kernel<__nv_bfloat16><<<(unsigned)n_ids, threads, 0, ctx->stream>>>(
-        (const __nv_bfloat16*)table, ids, vocab, (int)hidden, scale, (__nv_bfloat16*)out, ctx->status_dev);
-  else if (dtype == RB_F32)
-    embed_gather_kernel<float><<<(unsigned)n_ids, threads, 0, ctx->stream>>>((const float*)table, ids, vocab,
-                                                                            (int)hidden, scale, (float*)out,
-                                                                            ctx->status_dev);
-  else
-    return fail(RB_ERR_DTYPE, "rb_embed_gather: dtype %d unsupported", dtype);
+  if (dtype == RB_BF16) RB_TRY(embed_launch<__nv_bfloat16>(ctx, table, vocab, hidden, ids, n_ids, scale, out));
+  else if (dtype == RB_F32) RB_TRY(embed_launch<float>(ctx, table, vocab, hidden, ids, n_ids, scale, out));
+  else return fail(RB_ERR_DTYPE, "rb_embed_gather: dtype %d unsupported", dtype);
   ctx->launches++;
-  return launch_status("embed_gather");
+  return RB_OK;
+}
+
+template <typename T>
+static int norm_launch(rb_ctx* ctx, int kind, const void* x, const void* add, const float* acc, int n_acc,
+                       const void* acc_bias, const void* w, const void* b, float eps, int64_t rows, int64_t hidden,
+                       void* out, void* sum_out) {
+  const size_t acc_stride = (size_t)rows * hidden;
+  const bool vec_ok = (hidden % 8) == 0 && hidden <= 16384 && aligned16(x) && aligned16(add) && aligned16(acc) &&
+                      aligned16(acc_bias) && aligned16(w) && aligned16(b) && aligned16(out) && aligned16(sum_out) &&
+                      ((acc_stride * sizeof(float)) % 16) == 0;
+  if (vec_ok) {
+    const int nchunk = (int)(hidden / 8);
+    int threads = std::min(512, (nchunk + 31) / 32 * 32);
+    const int chunks = (nchunk + threads - 1) / threads;
+    auto go = [&](auto kern) {
+      return launch_kernel(kern, dim3((unsigned)rows), dim3(threads), 0, ctx->stream, ctx->pdl, kind, (const T*)x,
+                           (const T*)add, acc, n_acc, acc_stride, (const T*)acc_bias, (const T*)w, (const T*)b, eps,
+                           (int)hidden, (T*)out, (T*)sum_out);
+    };
+    if (chunks == 1) RB_CUDA(go(norm_vec_kernel<T, 1>));
+    else if (chunks == 2) RB_CUDA(go(norm_vec_kernel<T, 2>));
+    else RB_CUDA(go(norm_vec_kernel<T, 4>));
+    return RB_OK;
+  }
+  const size_t smem = (size_t)hidden * sizeof(float);
+  const int threads = hidden >= 2048 ? 512 : 256;
+  auto kern = norm_kernel<T>;
+  if (smem > 48 * 1024) RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  RB_CUDA(launch_kernel(kern, dim3((unsigned)rows), dim3(threads), smem, ctx->stream, ctx->pdl, kind, (const T*)x,
+                        (const T*)add, acc, n_acc, acc_stride, (const T*)acc_bias, (const T*)w, (const T*)b, eps,
+                        (int)hidden, (T*)out, (T*)sum_out));
+  return RB_OK;
 }
 
 extern "C" int32_t rb_norm(rb_ctx* ctx, int32_t kind, const void* x, const void* add, const float* acc, int32_t n_acc,
@@ -215,34 +497,21 @@ extern "C" int32_t rb_norm(rb_ctx* ctx, int32_t kind, const void* x, const void*
   RB_REQUIRE(out || sum_out, "rb_norm: no output given");
   RB_REQUIRE(kind >= RB_NORM_RMS && kind <= RB_NORM_LAYER, "rb_norm: bad kind %d", kind);
   RB_REQUIRE(!out || w || kind == RB_NORM_LAYER, "rb_norm: weight required");
-  RB_REQUIRE(rows >= 0 && hidden > 0 && hidden <= 49152 / 4 * 4, "rb_norm: hidden %lld out of range", (long long)hidden);
+  RB_REQUIRE(rows >= 0 && hidden > 0 && hidden <= 49152, "rb_norm: hidden %lld out of range", (long long)hidden);
   if (rows == 0) return RB_OK;
   if (!acc) n_acc = 0;
-  const size_t smem = (size_t)hidden * sizeof(float);
-  const int threads = hidden >= 2048 ? 512 : 256;
-  const size_t acc_stride = (size_t)rows * hidden;
+  if (n_acc == 0) acc = nullptr;
   ProfScope prof(ctx, RB_PROF_NORM,
                  (double)rows * hidden * (dtype_size(dtype) * ((x ? 1 : 0) + (add ? 1 : 0) + (out ? 1 : 0) + (sum_out ? 1 : 0)) + 4.0 * n_acc),
                  0.0);
-  if (dtype == RB_BF16) {
-    auto kern = norm_kernel<__nv_bfloat16>;
-    if (smem > 48 * 1024) RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<(unsigned)rows, threads, smem, ctx->stream>>>(kind, (const __nv_bfloat16*)x, (const __nv_bfloat16*)add, acc,
-                                                         n_acc, acc_stride, (const __nv_bfloat16*)acc_bias,
-                                                         (const __nv_bfloat16*)w, (const __nv_bfloat16*)b, eps,
-                                                         (int)hidden, (__nv_bfloat16*)out, (__nv_bfloat16*)sum_out);
-  } else if (dtype == RB_F32) {
-    auto kern = norm_kernel<float>;
-    if (smem > 48 * 1024) RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<(unsigned)rows, threads, smem, ctx->stream>>>(kind, (const float*)x, (const float*)add, acc, n_acc,
-                                                         acc_stride, (const float*)acc_bias, (const float*)w,
-                                                         (const float*)b, eps, (int)hidden, (float*)out,
-                                                         (float*)sum_out);
-  } else {
+  if (dtype == RB_BF16)
+    RB_TRY(norm_launch<__nv_bfloat16>(ctx, kind, x, add, acc, n_acc, acc_bias, w, b, eps, rows, hidden, out, sum_out));
+  else if (dtype == RB_F32)
+    RB_TRY(norm_launch<float>(ctx, kind, x, add, acc, n_acc, acc_bias, w, b, eps, rows, hidden, out, sum_out));
+  else
     return fail(RB_ERR_DTYPE, "rb_norm: dtype %d unsupported", dtype);
-  }
   ctx->launches++;
-  return launch_status("norm");
+  return RB_OK;
 }
 
 extern "C" int32_t rb_rope_tables(rb_ctx* ctx, int32_t recipe, int32_t rot_dim, int32_t max_pos, double theta,
@@ -273,6 +542,37 @@ extern "C" int32_t rb_rope_tables(rb_ctx* ctx, int32_t recipe, int32_t rot_dim, 
   return RB_OK;
 }
 
+template <typename T>
+static int rope_launch(rb_ctx* ctx, const void* qkv, const float* acc, int n_acc, const void* bias, const float* cos_t,
+                       const float* sin_t, int rot, int batch, int s_new, int q_heads, rb_kv_cache* c, int layer,
+                       void* q_out) {
+  const int d = c->head_dim, ncol = (q_heads + 2 * c->kv_heads) * d;
+  const size_t acc_stride = (size_t)batch * s_new * ncol;
+  const size_t loff = (size_t)layer * c->layer_stride_elems();
+  T* kc = (T*)c->k + loff;
+  T* vc = (T*)c->v + loff;
+  const int half = rot / 2;
+  const bool vec_ok = (d % 8) == 0 && (half % 8) == 0 && aligned16(qkv) && aligned16(acc) && aligned16(bias) &&
+                      aligned16(q_out) && aligned16(cos_t) && aligned16(sin_t) && ((acc_stride * sizeof(float)) % 16) == 0;
+  if (vec_ok) {
+    const int items = (q_heads + c->kv_heads) * (half / 8 + (d - rot) / 8) + c->kv_heads * (d / 8);
+    const int threads = std::min(512, (items + 31) / 32 * 32);
+    RB_CUDA(launch_kernel(rope_kv_append_vec_kernel<T>, dim3((unsigned)(batch * s_new)), dim3(threads), 0, ctx->stream,
+                          ctx->pdl, (const T*)qkv, acc, n_acc, acc_stride, (const T*)bias, cos_t, sin_t, rot, s_new,
+                          q_heads, c->kv_heads, d, (T*)q_out, kc, vc, (const int32_t*)c->block_table,
+                          (const int32_t*)c->seq_lens, c->pages_per_seq, c->max_seq, ctx->status_dev));
+    return RB_OK;
+  }
+  const size_t smem = (size_t)ncol * sizeof(float);
+  auto kern = rope_kv_append_kernel<T>;
+  if (smem > 48 * 1024) RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  RB_CUDA(launch_kernel(kern, dim3((unsigned)(batch * s_new)), dim3(256), smem, ctx->stream, ctx->pdl, (const T*)qkv, acc,
+                        n_acc, acc_stride, (const T*)bias, cos_t, sin_t, rot, s_new, q_heads, c->kv_heads, d, (T*)q_out,
+                        kc, vc, (const int32_t*)c->block_table, (const int32_t*)c->seq_lens, c->pages_per_seq,
+                        c->max_seq, ctx->status_dev));
+  return RB_OK;
+}
+
 extern "C" int32_t rb_rope_kv_append(rb_ctx* ctx, const void* qkv, const float* acc, int32_t n_acc, const void* bias,
                                      const float* cos_t, const float* sin_t, int32_t rot, int32_t batch, int32_t s_new,
                                      int32_t q_heads, rb_kv_cache* c, int32_t layer, void* q_out, int32_t dtype) {
@@ -283,32 +583,31 @@ extern "C" int32_t rb_rope_kv_append(rb_ctx* ctx, const void* qkv, const float* 
   RB_REQUIRE(batch > 0 && batch <= c->max_batch && s_new > 0, "rb_rope_kv_append: bad batch/seq");
   RB_REQUIRE(rot >= 0 && rot <= c->head_dim && (rot % 2) == 0, "rb_rope_kv_append: bad rotary dim %d", rot);
   if (!acc) n_acc = 0;
-  const int d = c->head_dim, ncol = (q_heads + 2 * c->kv_heads) * d;
-  const size_t smem = (size_t)ncol * sizeof(float);
-  const size_t acc_stride = (size_t)batch * s_new * ncol;
-  const size_t loff = (size_t)layer * c->layer_stride_elems();
-  const int threads = 256;
+  if (n_acc == 0) acc = nullptr;
+  const int ncol = (q_heads + 2 * c->kv_heads) * c->head_dim;
   ProfScope prof(ctx, RB_PROF_ROPE_KV, (double)batch * s_new * ncol * (dtype_size(dtype) * (qkv ? 2.0 : 1.0) + 4.0 * n_acc), 0.0);
-  if (dtype == RB_BF16) {
-    auto kern = rope_kv_append_kernel<__nv_bfloat16>;
-    if (smem > 48 * 1024) RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<batch * s_new, threads, smem, ctx->stream>>>(
-        (const __nv_bfloat16*)qkv, acc, n_acc, acc_stride, (const __nv_bfloat16*)bias, cos_t, sin_t, rot, s_new,
-        q_heads, c->kv_heads, d, (__nv_bfloat16*)q_out, (__nv_bfloat16*)c->k + loff, (__nv_bfloat16*)c->v + loff,
-        c->block_table, c->seq_lens, c->pages_per_seq, c->max_seq, ctx->status_dev);
-  } else if (dtype == RB_F32) {
-    auto kern = rope_kv_append_kernel<float>;
-    if (smem > 48 * 1024) RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<batch * s_new, threads, smem, ctx->stream>>>((const float*)qkv, acc, n_acc, acc_stride, (const float*)bias,
-                                                        cos_t, sin_t, rot, s_new, q_heads, c->kv_heads, d,
-                                                        (float*)q_out, (float*)c->k + loff, (float*)c->v + loff,
-                                                        c->block_table, c->seq_lens, c->pages_per_seq, c->max_seq,
-                                                        ctx->status_dev);
-  } else {
+  if (dtype == RB_BF16)
+    RB_TRY(rope_launch<__nv_bfloat16>(ctx, qkv, acc, n_acc, bias, cos_t, sin_t, rot, batch, s_new, q_heads, c, layer, q_out));
+  else if (dtype == RB_F32)
+    RB_TRY(rope_launch<float>(ctx, qkv, acc, n_acc, bias, cos_t, sin_t, rot, batch, s_new, q_heads, c, layer, q_out));
+  else
     return fail(RB_ERR_DTYPE, "rb_rope_kv_append: dtype %d unsupported", dtype);
-  }
   ctx->launches++;
-  return launch_status("rope_kv_append");
+  return RB_OK;
+}
+
+template <typename T>
+static int argmax_launch(rb_ctx* ctx, const void* logits, int64_t rows, int64_t cols, uint32_t* out) {
+  // enough blocks per row to fill the GPU, at least ~2K elements each
+  int per_row = (int)std::min<int64_t>(std::max<int64_t>(1, (2 * ctx->sm_count + rows - 1) / rows), (cols + 2047) / 2048);
+  per_row = std::max(1, std::min(per_row, 64));
+  for (int64_t r0 = 0; r0 < rows; r0 += kArgmaxRows) {
+    const int64_t n = std::min<int64_t>(kArgmaxRows, rows - r0);
+    RB_CUDA(launch_kernel(argmax_rows_kernel<T>, dim3((unsigned)per_row, (unsigned)n), dim3(256), 0, ctx->stream, ctx->pdl,
+                          (const T*)logits + r0 * cols, cols, out + r0, ctx->argmax_best, ctx->argmax_count));
+    ctx->launches++;
+  }
+  return RB_OK;
 }
 
 extern "C" int32_t rb_argmax_rows(rb_ctx* ctx, const void* logits, int32_t dtype, int64_t rows, int64_t cols,
@@ -317,12 +616,7 @@ extern "C" int32_t rb_argmax_rows(rb_ctx* ctx, const void* logits, int32_t dtype
   RB_REQUIRE(rows >= 0 && cols > 0 && cols <= 0xffffffffLL, "rb_argmax_rows: bad sizes");
   if (rows == 0) return RB_OK;
   ProfScope prof(ctx, RB_PROF_ARGMAX, (double)rows * cols * dtype_size(dtype), 0.0);
-  if (dtype == RB_BF16)
-    argmax_rows_kernel<__nv_bfloat16><<<(unsigned)rows, 1024, 0, ctx->stream>>>((const __nv_bfloat16*)logits, cols, out);
-  else if (dtype == RB_F32)
-    argmax_rows_kernel<float><<<(unsigned)rows, 1024, 0, ctx->stream>>>((const float*)logits, cols, out);
-  else
-    return fail(RB_ERR_DTYPE, "rb_argmax_rows: dtype %d unsupported", dtype);
-  ctx->launches++;
-  return launch_status("argmax_rows");
+  if (dtype == RB_BF16) return argmax_launch<__nv_bfloat16>(ctx, logits, rows, cols, out);
+  if (dtype == RB_F32) return argmax_launch<float>(ctx, logits, rows, cols, out);
+  return fail(RB_ERR_DTYPE, "rb_argmax_rows: dtype %d unsupported", dtype);
 }

@@ -149,9 +149,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   ptx::tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
 
+  pdl_launch_dependents();
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      // The weight operand does not depend on the kernel before this one: its first ring of
+      // stages is requested right away, and only then does the producer wait for the predecessor
+      // before it requests the matching activation tiles.  On a chain of decode-sized GEMMs this
+      // hides the launch, set-up and pipeline-fill latency behind the previous kernel.
+      auto load_weights = [&](uint8_t* st, int stage, int kb, int pt, int qt) {
+        if (SWAP) {
+          ptx::tma_load_2d(st, &tm_p, &full_bar[stage], kb * kBK, pt * kBM);
+          if (C::kPTiles == 2) ptx::tma_load_2d(st + C::kPBytes, &tm_p2, &full_bar[stage], kb * kBK, pt * kBM);
+        } else {
+          uint8_t* qs = st + C::kPTiles * C::kPBytes;
+          ptx::tma_load_2d(qs, &tm_q, &full_bar[stage], kb * kBK, qt * BN);
+          if (C::kQTiles == 2) ptx::tma_load_2d(qs + C::kQBytes, &tm_q2, &full_bar[stage], kb * kBK, qt * BN);
+        }
+      };
+      auto load_activations = [&](uint8_t* st, int stage, int kb, int pt, int qt) {
+        if (SWAP) ptx::tma_load_2d(st + C::kPTiles * C::kPBytes, &tm_q, &full_bar[stage], kb * kBK, qt * BN);
+        else ptx::tma_load_2d(st, &tm_p, &full_bar[stage], kb * kBK, pt * kBM);
+      };
+      int n_pre = 0;
+      for (int item = blockIdx.x; item < p.n_items && n_pre < C::kStages; item += gridDim.x) {
+        int pt, qt, split;
+        decode_item(p, item, SWAP, pt, qt, split);
+        const int kb0 = split * p.kb_per_split, kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1 && n_pre < C::kStages; ++kb, ++n_pre) {
+          ptx::mbar_expect_tx(&full_bar[n_pre], C::kStageBytes);
+          load_weights(tiles + (size_t)n_pre * C::kStageBytes, n_pre, kb, pt, qt);
+        }
+      }
+      pdl_wait();
       int stage = 0;
       uint32_t phase = 0;
       uint32_t issued = 0;
@@ -161,14 +191,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
         decode_item(p, item, SWAP, pt, qt, split);
         const int kb0 = split * p.kb_per_split, kb1 = min(p.num_kb, kb0 + p.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_flag)) { ok = false; break; }
           uint8_t* st = tiles + (size_t)stage * C::kStageBytes;
-          ptx::mbar_expect_tx(&full_bar[stage], C::kStageBytes);
-          ptx::tma_load_2d(st, &tm_p, &full_bar[stage], kb * kBK, pt * kBM);
-          if (C::kPTiles == 2) ptx::tma_load_2d(st + C::kPBytes, &tm_p2, &full_bar[stage], kb * kBK, pt * kBM);
-          uint8_t* qs = st + C::kPTiles * C::kPBytes;
-          ptx::tma_load_2d(qs, &tm_q, &full_bar[stage], kb * kBK, qt * BN);
-          if (C::kQTiles == 2) ptx::tma_load_2d(qs + C::kQBytes, &tm_q2, &full_bar[stage], kb * kBK, qt * BN);
+          if ((int)issued >= n_pre) {
+            if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_flag)) { ok = false; break; }
+            ptx::mbar_expect_tx(&full_bar[stage], C::kStageBytes);
+            load_weights(st, stage, kb, pt, qt);
+          }
+          load_activations(st, stage, kb, pt, qt);
           ++issued;
           if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
         }
@@ -218,6 +247,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
+    pdl_wait();  // bias/residual reads and every store below must follow the predecessor's completion
     const int quarter = warp & 3;              // the 32 TMEM lanes this warp may read
     const int lane_row = quarter * 32 + lane;  // row of the P operand inside the tile
     int as = 0;
@@ -390,9 +420,10 @@ int launch(rb_ctx* ctx, const GemmArgs& a, Params& p) {
     attr_set = true;
   }
   const int grid = std::min(p.n_items, ctx->sm_count);
-  kern<<<grid, kThreads, C::kSmemBytes, ctx->stream>>>(*tp, *tp2, *tq, *tq2, p);
+  RB_CUDA(launch_kernel(kern, dim3((unsigned)grid), dim3(kThreads), (size_t)C::kSmemBytes, ctx->stream, ctx->pdl, *tp, *tp2,
+                        *tq, *tq2, p));
   ctx->launches++;
-  return launch_status("gemm_tc");
+  return RB_OK;
 }
 
 }  // namespace
