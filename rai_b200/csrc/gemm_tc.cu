@@ -22,7 +22,10 @@
 //
 // Every barrier wait is bounded; a give-up is recorded in the context's status word and the CTA
 // drains its in-flight copies, frees its TMEM and returns.
+#include <stdlib.h>
+
 #include <algorithm>
+#include <vector>
 
 #include "ctx.h"
 #include "ptx.cuh"
@@ -70,7 +73,15 @@ struct Params {
   float* part;
   int act;
   uint32_t* status;
+  unsigned long long* trace;  // debugging aid: 8 timestamps per CTA when non-null
 };
+
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define RB_TRACE(slot) do { if (p.trace) p.trace[(size_t)blockIdx.x * 8 + (slot)] = gtime(); } while (0)
 
 __device__ __forceinline__ void decode_item(const Params& p, int item, bool swap, int& pt, int& qt, int& split) {
   if (swap) {
@@ -113,6 +124,39 @@ __device__ __forceinline__ void unpack8(const uint4& u, float* v) {
   }
 }
 
+constexpr int kEpiPitch = kBM + 8;  // elements; keeps the 16-byte row reads of the staging tile conflict-free
+
+// Barrier among the 128 epilogue threads only (hardware barrier 1; __syncthreads is barrier 0).
+__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Activation over a register array with the selector hoisted out of the element loop
+// (rai-core/src/hlops/activations.rs:20-32); fast-math forms, results are rounded to bf16 anyway.
+template <int N>
+__device__ __forceinline__ void act_inplace(int act, float (&v)[N]) {
+  if (act == RB_ACT_SILU) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) v[i] = __fdividef(v[i], 1.0f + __expf(-v[i]));
+  } else if (act == RB_ACT_GELU_TANH) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      const float x = v[i];
+      v[i] = 0.5f * x * (1.0f + tanh_fast(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    }
+  } else if (act == RB_ACT_GELU_ERF) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) v[i] = v[i] * 0.5f * (1.0f + erff(v[i] * 0.7071067811865476f));
+  } else if (act == RB_ACT_RELU) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) v[i] = fmaxf(v[i], 0.f);
+  }
+}
+
 template <int BN, bool SWAP, bool GATED>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_p2,
@@ -126,8 +170,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile uint32_t abort_flag;
   __shared__ uint32_t issued_count;  // stages the producer has handed to the copy engine
+  __shared__ volatile uint32_t epi_ok[4];
+  __shared__ __align__(16) bf16 epi_tile[32 * kEpiPitch];  // 32 output rows x 128 columns, padded
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) RB_TRACE(0);
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
   if (threadIdx.x == 0) {
@@ -148,6 +195,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
+  if (threadIdx.x == 0) RB_TRACE(1);
 
   pdl_launch_dependents();
   if (warp == 0) {
@@ -181,7 +229,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           load_weights(tiles + (size_t)n_pre * C::kStageBytes, n_pre, kb, pt, qt);
         }
       }
+      RB_TRACE(2);
       pdl_wait();
+      RB_TRACE(3);
       int stage = 0;
       uint32_t phase = 0;
       uint32_t issued = 0;
@@ -203,6 +253,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
         }
       }
       issued_count = issued;
+      RB_TRACE(4);
       if (!ok) { p.status[0] = (uint32_t)(-RB_ERR_TIMEOUT); p.status[1] = 0x6E01u; p.status[2] = blockIdx.x; }
     }
   } else if (warp == 1) {
@@ -241,6 +292,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
         }
         if (!ok) break;
         ptx::umma_commit(&acc_full[as]);
+        RB_TRACE(5);
         if (++as == 2) { as = 0; aphase ^= 1u; }
       }
       if (!ok) { p.status[0] = (uint32_t)(-RB_ERR_TIMEOUT); p.status[1] = 0x6E02u; p.status[2] = blockIdx.x; }
@@ -262,8 +314,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           for (int gm = qt * BN; gm < min(p.m, (qt + 1) * BN); ++gm) p.part[((size_t)split * p.m + gm) * p.n + gn] = 0.f;
         continue;
       }
-      if (!ptx::mbar_wait(&acc_full[as], aphase, &abort_flag)) { ok = false; break; }
+      // The four epilogue warps meet at named barriers below, so they must agree on giving up.
+      const bool mine = ptx::mbar_wait(&acc_full[as], aphase, &abort_flag);
+      if (lane == 0) epi_ok[warp - 2] = mine ? 1u : 0u;
+      epi_barrier();
+      const bool all_ok = (epi_ok[0] & epi_ok[1] & epi_ok[2] & epi_ok[3]) != 0u;
+      epi_barrier();
+      if (!all_ok) { ok = false; break; }
       ptx::tc_fence_after();
+      if (threadIdx.x == 64) RB_TRACE(6);
       const uint32_t t0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * C::kAccCols);
       constexpr int CH = BN >= 32 ? 32 : 16;  // columns per TMEM load
 #pragma unroll 1
@@ -287,28 +346,63 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
         // here: GATED ? (g = gate product, v = up product) : (v = product)
         if (SWAP) {
           const int gn = pt * kBM + lane_row;  // output column = weight row
-          if (gn < p.n) {
-            const float bias = (!GATED && p.bias) ? __bfloat162float(p.bias[gn]) : 0.f;
+          if (p.part) {
+            if (gn < p.n) {
 #pragma unroll
-            for (int j = 0; j < CH; ++j) {
-              const int gm = qt * BN + c0 + j;
-              if (gm >= p.m) break;
-              if (p.part) {
-                p.part[((size_t)split * p.m + gm) * p.n + gn] = v[j];
-              } else {
-                float y;
-                if (GATED) y = act_apply(p.act, g[j]) * v[j];
-                else {
-                  y = act_apply(p.act, v[j] + bias);
-                  if (p.residual) y += __bfloat162float(p.residual[(size_t)gm * p.n + gn]);
-                }
-                p.out[(size_t)gm * p.n + gn] = __float2bfloat16_rn(y);
+              for (int j = 0; j < CH; ++j) {
+                const int gm = qt * BN + c0 + j;
+                if (gm < p.m) p.part[((size_t)split * p.m + gm) * p.n + gn] = v[j];
               }
             }
+          } else {
+            if (GATED) {
+              act_inplace(p.act, g);
+#pragma unroll
+              for (int j = 0; j < CH; ++j) v[j] *= g[j];
+            } else {
+              const float bias = (p.bias && gn < p.n) ? __bfloat162float(p.bias[gn]) : 0.f;
+#pragma unroll
+              for (int j = 0; j < CH; ++j) v[j] += bias;
+              act_inplace(p.act, v);
+            }
+            // The accumulator holds the tile transposed (lane = output column).  Turn it through
+            // shared memory so that the global stores are 16-byte pieces of output rows.
+#pragma unroll
+            for (int j = 0; j < CH; ++j) epi_tile[j * kEpiPitch + lane_row] = __float2bfloat16_rn(v[j]);
+            epi_barrier();
+            const int et = threadIdx.x - 64;
+            const bool vec_ok = (p.n % 8) == 0;
+            for (int id = et; id < CH * (kBM / 8); id += 128) {
+              const int j = id / (kBM / 8), c8 = (id % (kBM / 8)) * 8;
+              const int gm = qt * BN + c0 + j, gn8 = pt * kBM + c8;
+              if (gm >= p.m || gn8 >= p.n) continue;
+              uint4 u = *reinterpret_cast<const uint4*>(epi_tile + j * kEpiPitch + c8);
+              bf16* dst = p.out + (size_t)gm * p.n + gn8;
+              if (vec_ok) {
+                if (!GATED && p.residual) {
+                  float a8[8], r8[8];
+                  unpack8(u, a8);
+                  unpack8(*reinterpret_cast<const uint4*>(p.residual + (size_t)gm * p.n + gn8), r8);
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) a8[i] += r8[i];
+                  u = pack8(a8);
+                }
+                *reinterpret_cast<uint4*>(dst) = u;
+              } else {
+                const bf16* e = reinterpret_cast<const bf16*>(&u);
+                for (int i = 0; i < 8 && gn8 + i < p.n; ++i) {
+                  float y = __bfloat162float(e[i]);
+                  if (!GATED && p.residual) y += __bfloat162float(p.residual[(size_t)gm * p.n + gn8 + i]);
+                  dst[i] = __float2bfloat16_rn(y);
+                }
+              }
+            }
+            epi_barrier();  // the staging tile is rewritten by the next chunk
           }
         } else {
           const int gm = pt * kBM + lane_row;
           const int gn0 = qt * BN + c0;
+          if (GATED) act_inplace(p.act, g);
           if (gm < p.m) {
             const bool vec_ok = (p.n % 8) == 0;
 #pragma unroll
@@ -318,7 +412,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
               float y[8];
               if (GATED) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) y[j] = act_apply(p.act, g[j8 + j]) * v[j8 + j];
+                for (int j = 0; j < 8; ++j) y[j] = g[j8 + j] * v[j8 + j];  // g already holds act(gate)
               } else {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) y[j] = v[j8 + j];
@@ -332,8 +426,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
                     for (int j = 0; j < 8 && gn + j < p.n; ++j) y[j] += __bfloat162float(p.bias[gn + j]);
                   }
                 }
-#pragma unroll
-                for (int j = 0; j < 8; ++j) y[j] = act_apply(p.act, y[j]);
+                act_inplace(p.act, y);
                 if (p.residual) {
                   if (vec_ok) {
                     float r8[8];
@@ -357,6 +450,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
       }
       ptx::tc_fence_before();
       __syncwarp();
+      if (threadIdx.x == 64) RB_TRACE(7);
       if (lane == 0) ptx::mbar_arrive(&acc_empty[as]);
       if (++as == 2) { as = 0; aphase ^= 1u; }
     }
@@ -420,6 +514,33 @@ int launch(rb_ctx* ctx, const GemmArgs& a, Params& p) {
     attr_set = true;
   }
   const int grid = std::min(p.n_items, ctx->sm_count);
+  static const bool trace = getenv("RAI_B200_GEMM_TRACE") != nullptr;
+  if (trace) {  // debugging aid: synchronous, prints per-phase timing of this launch
+    unsigned long long* tr = nullptr;
+    RB_CUDA(cudaMalloc(&tr, (size_t)grid * 8 * sizeof(unsigned long long)));
+    RB_CUDA(cudaMemset(tr, 0, (size_t)grid * 8 * sizeof(unsigned long long)));
+    p.trace = tr;
+    RB_CUDA(launch_kernel(kern, dim3((unsigned)grid), dim3(kThreads), (size_t)C::kSmemBytes, ctx->stream, false, *tp, *tp2,
+                          *tq, *tq2, p));
+    RB_CUDA(cudaStreamSynchronize(ctx->stream));
+    std::vector<unsigned long long> h((size_t)grid * 8);
+    RB_CUDA(cudaMemcpy(h.data(), tr, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    cudaFree(tr);
+    unsigned long long t0 = ~0ull;
+    for (int c = 0; c < grid; ++c) t0 = std::min(t0, h[c * 8]);
+    double mx[8] = {0}, av[8] = {0};
+    for (int c = 0; c < grid; ++c)
+      for (int i = 0; i < 8; ++i) {
+        const double d = h[c * 8 + i] ? (double)(h[c * 8 + i] - t0) / 1e3 : 0.0;
+        mx[i] = std::max(mx[i], d); av[i] += d / grid;
+      }
+    fprintf(stderr, "gemm_tc<%d,%d,%d> m=%d n=%d k=%d items=%d grid=%d | us since first CTA (avg/max): start %.1f/%.1f  setup %.1f/%.1f  "
+            "prefetched %.1f/%.1f  dep-wait %.1f/%.1f  issued-all %.1f/%.1f  last-mma-commit %.1f/%.1f  epi-begin %.1f/%.1f  epi-end %.1f/%.1f\n",
+            BN, (int)SWAP, (int)GATED, p.m, p.n, p.k, p.n_items, grid, av[0], mx[0], av[1], mx[1], av[2], mx[2], av[3], mx[3], av[4], mx[4],
+            av[5], mx[5], av[6], mx[6], av[7], mx[7]);
+    ctx->launches++;
+    return RB_OK;
+  }
   RB_CUDA(launch_kernel(kern, dim3((unsigned)grid), dim3(kThreads), (size_t)C::kSmemBytes, ctx->stream, ctx->pdl, *tp, *tp2,
                         *tq, *tq2, p));
   ctx->launches++;
