@@ -205,10 +205,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
       // stages is requested right away, and only then does the producer wait for the predecessor
       // before it requests the matching activation tiles.  On a chain of decode-sized GEMMs this
       // hides the launch, set-up and pipeline-fill latency behind the previous kernel.
+      // decode-sized GEMMs read every weight byte exactly once: evict-first keeps them from pushing
+      // the activations and split-K partials out of L2
+      const uint64_t stream_policy = ptx::policy_evict_first();
       auto load_weights = [&](uint8_t* st, int stage, int kb, int pt, int qt) {
         if (SWAP) {
-          ptx::tma_load_2d(st, &tm_p, &full_bar[stage], kb * kBK, pt * kBM);
-          if (C::kPTiles == 2) ptx::tma_load_2d(st + C::kPBytes, &tm_p2, &full_bar[stage], kb * kBK, pt * kBM);
+          ptx::tma_load_2d_hint(st, &tm_p, &full_bar[stage], kb * kBK, pt * kBM, stream_policy);
+          if (C::kPTiles == 2)
+            ptx::tma_load_2d_hint(st + C::kPBytes, &tm_p2, &full_bar[stage], kb * kBK, pt * kBM, stream_policy);
         } else {
           uint8_t* qs = st + C::kPTiles * C::kPBytes;
           ptx::tma_load_2d(qs, &tm_q, &full_bar[stage], kb * kBK, qt * BN);
