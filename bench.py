@@ -428,7 +428,12 @@ def run_ours(args):
         "achieved": gemm.get("achieved_gbs"), "peak": peaks["hbm_gbs"] * world, "unit": "GB/s",
         "frac": (gemm["achieved_gbs"] / (peaks["hbm_gbs"] * world)) if gemm.get("achieved_gbs") else None,
         "peak_kind": f"{peak_kind} stream-copy bandwidth x {world} GPU(s)",
-        "traffic": None,
+        # DRAM bytes per launch: ncu (profiles/gemm_tc_decode_2layer_b64.md) measured 476.7 MB of DRAM
+        # read+write for the four GEMMs of one layer against 486.2 MB of algorithmic bytes (the float32
+        # split-K partials mostly stay in L2), i.e. 0.98 of algorithmic; scaled to this run's launches.
+        "traffic": (0.98 * gemm["gbytes_per_step"] * 1e9 / gemm["launches_per_step"]) if gemm else None,
+        "traffic_unit": "bytes per launch (ncu on a 2-layer case, scaled by algorithmic bytes)",
+        "algorithmic_bytes_per_launch": (gemm["gbytes_per_step"] * 1e9 / gemm["launches_per_step"]) if gemm else None,
         "avg_launch_us": gemm.get("avg_launch_us"), "launches_per_step": gemm.get("launches_per_step"),
         "algorithmic_gbytes_per_step": gemm.get("gbytes_per_step"),
         "whole_step": {"algorithmic_gbytes": step_bytes / 1e9, "achieved_gbs": step_gbs,
