@@ -1,0 +1,65 @@
+"""Run under torch.distributed.run with N ranks (one GPU each): tensor-parallel forward of tiny
+decoders through the C ABI against the CPU oracle.  Exits non-zero on mismatch.  Used by
+tests/test_gpu_50_tp.py; NCCL's in-switch reduction is switched off by the caller."""
+import ctypes
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+for p in (ROOT, os.path.join(ROOT, "oracle"), HERE):
+    sys.path.insert(0, p)
+
+import rai_cpu  # noqa: E402
+import util  # noqa: E402
+from rai_b200 import _lib, configs, synth  # noqa: E402
+from rai_b200.device import Cuda  # noqa: E402
+from rai_b200.models import Model  # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("gloo")   # rendezvous and id exchange only; the data path is the library's NCCL
+    dev = Cuda(local)
+    failures = []
+    for name, dtype, tol in (("tiny-qwen2", _lib.F32, 1e-4), ("tiny-qwen2", _lib.BF16, 2e-2),
+                             ("tiny-qwen2-g7", _lib.BF16, 2e-2), ("tiny-phi2", _lib.BF16, 2e-2),
+                             ("tiny-phi3", _lib.BF16, 2e-2), ("tiny-gemma", _lib.BF16, 2e-2)):
+        cfg = configs.get(name)
+        nkv = cfg.get("num_key_value_heads") or cfg["num_attention_heads"]
+        if not ((world <= nkv and nkv % world == 0) or (world > nkv and world % nkv == 0)):
+            continue
+        if cfg["intermediate_size"] % world or cfg["vocab_size"] % world:
+            continue
+        w = synth.weights(cfg, 31)
+        prompt = synth.prompt(cfg, 2, 40, 31)
+        m = Model(cfg, dtype, dev, 2, 128, tp_rank=rank, tp_size=world)
+        uid = [None]
+        if rank == 0:
+            buf = ctypes.create_string_buffer(128)
+            _lib.call("rb_tp_unique_id", buf)
+            uid = [buf.raw]
+        dist.broadcast_object_list(uid, 0)
+        m.tp_init(uid[0])
+        m.update_params(w)
+        got, logits = m.greedy_generate(prompt, 6, collect_logits=True)
+        if rank == 0:
+            want, ref = rai_cpu.greedy_generate(util.build_oracle(cfg, w), torch.from_numpy(prompt.astype(np.int64)), 6, True)
+            err = util.logit_error(logits[0], ref[0]) if dtype == _lib.BF16 else util.rel_error(logits[0], ref[0])
+            same = bool((got.numpy() == want.numpy()).all())
+            print(f"tp{world} {name} dtype {dtype}: prefill logits error {err:.2e}, greedy tokens identical {same}", flush=True)
+            if err > tol or (dtype == _lib.F32 and not same):
+                failures.append(name)
+        m.close()
+        dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(1 if failures else 0)
+
+
+if __name__ == "__main__":
+    main()
