@@ -168,6 +168,22 @@ int32_t rb_rope_kv_append(rb_ctx* ctx, const void* qkv_dev, const float* acc_dev
 int32_t rb_attention(rb_ctx* ctx, const void* q_dev, rb_kv_cache* cache, int32_t layer, int32_t batch, int32_t s_new,
                      int32_t q_heads, float scale, void* out_dev, int32_t dtype);
 
+/* No counterpart in the reference.  Single-token (decode) attention like rb_attention with s_new = 1,
+ * bf16 only, for callers that must not trigger a device allocation: rb_attention grows its split-KV
+ * scratch with cudaMalloc when a larger shape arrives, which is off limits to a host runtime that owns
+ * all device memory through its own pool, and unwelcome in a serving loop because an allocation can
+ * synchronise the whole device.  This variant keeps that scratch in a 4 MiB array built into the
+ * library (held by every GPU that loads it, until exit) and calls no allocator of any kind.
+ *   - limit: batch * q_heads * splits * (head_dim + 2) floats must fit in 1 Mi floats; larger shapes are
+ *     rejected with RB_ERR_INVALID and a message naming the sizes (use rb_attention for those);
+ *   - the first call on a device looks up the array's device address (one cudaGetSymbolAddress, the
+ *     context's device must be current); make that first call before any stream capture;
+ *   - all calls share the one array: two calls whose kernels overlap on the GPU (different streams or
+ *     contexts of one process) race on it; calls on one stream are safe.  Nothing in it needs to start at
+ *     zero: every slot a call reads was written by that call. */
+int32_t rb_attention_decode_static(rb_ctx* ctx, const void* q_dev, rb_kv_cache* cache, int32_t layer, int32_t batch,
+                                   int32_t q_heads, float scale, void* out_dev);
+
 /* sample_argmax, examples/qwen2/src/main.rs:32-40: per row, the index of the maximum under f32
  * total order, the LAST index among equal maxima.  Bit-exact by construction. */
 int32_t rb_argmax_rows(rb_ctx* ctx, const void* logits_dev, int32_t dtype, int64_t rows, int64_t cols,

@@ -403,6 +403,56 @@ int launch_attention(rb_ctx* ctx, AParams& p, int batch, int max_len) {
 
 }  // namespace
 
+// ------------------------------------------------------------------------------------------
+// Decode attention that allocates nothing.  The split-KV partials (per sequence, head and split:
+// head_dim running sums plus a max and a sum) normally live in a buffer that the library grows
+// with cudaMalloc when a larger shape arrives.  Some callers cannot have that happen under them:
+// a host runtime that hands all device memory to its own pool and treats a foreign cudaMalloc as
+// an error, or a serving loop that cannot afford the device-wide synchronisation an allocation may
+// imply.  For them the same kernels run here with the partials in a fixed array that is part of
+// the library image: every GPU that loads the library holds these 4 MiB until the process exits.
+// ------------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchFloats = 1u << 20;  // 4 MiB
+static __device__ __align__(256) float g_static_attn_scratch[kStaticScratchFloats];
+// In host code the array's name is only a handle for the runtime, not a device address: the address
+// the kernels need is asked for once per device (with that device current) and kept here.
+static float* g_static_attn_scratch_dev[64] = {};
+
+template <int D>
+static int launch_attention_decode_static(rb_ctx* ctx, AParams& p, int batch, int max_len, float* scratch) {
+  using C = ACfg<D, true>;
+  auto kern = attention_kernel<D, true>;
+  RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+  const int tiles = std::max(1, (max_len + kTile - 1) / kTile);
+  const int work = batch * p.kv_heads;
+  const int slots = 2 * ctx->sm_count;
+  int splits = 1;
+  if (work * 4 < slots * 3) {
+    splits = (slots + work - 1) / work;
+    splits = std::max(1, std::min(splits, std::min(tiles / 2, 32)));
+  }
+  p.n_splits = splits;
+  if (splits > 1) {
+    const size_t need = (size_t)batch * p.q_heads * splits * (D + 2);
+    if (need > kStaticScratchFloats)
+      return fail(RB_ERR_INVALID,
+                  "rb_attention_decode_static: batch %d x %d heads x %d splits x head_dim %d needs %zu scratch floats, "
+                  "the built-in array holds %zu; use rb_attention",
+                  batch, p.q_heads, splits, D, need, kStaticScratchFloats);
+    p.part_o = scratch;
+    p.part_ml = scratch + (size_t)batch * p.q_heads * splits * D;
+  }
+  dim3 grid((unsigned)splits, (unsigned)p.kv_heads, (unsigned)batch);
+  RB_CUDA(launch_kernel(kern, grid, dim3(128), (size_t)C::kSmemBytes, ctx->stream, ctx->pdl, p));
+  ctx->launches++;
+  if (splits > 1) {
+    RB_CUDA(launch_kernel(attention_merge_kernel, dim3((unsigned)(batch * p.q_heads)), dim3(128), 0, ctx->stream, ctx->pdl,
+                          (const float*)p.part_o, (const float*)p.part_ml, splits, D, p.out));
+    ctx->launches++;
+  }
+  return RB_OK;
+}
+
 int attention_mma_bf16(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, int batch, int s_new, int q_heads,
                        float scale, void* out) {
   AParams p{};
@@ -435,3 +485,52 @@ int attention_mma_bf16(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, in
 }
 
 }  // namespace rb
+
+extern "C" int32_t rb_attention_decode_static(rb_ctx* ctx, const void* q, rb_kv_cache* c, int32_t layer, int32_t batch,
+                                              int32_t q_heads, float scale, void* out) {
+  using namespace rb;
+  RB_REQUIRE(ctx && q && c && out, "rb_attention_decode_static: null argument");
+  RB_REQUIRE(c->dtype == RB_BF16, "rb_attention_decode_static: bf16 caches only");
+  RB_REQUIRE(layer >= 0 && layer < c->layers, "rb_attention_decode_static: layer %d out of range", layer);
+  RB_REQUIRE(batch > 0 && batch <= c->max_batch, "rb_attention_decode_static: bad batch");
+  RB_REQUIRE(q_heads > 0 && q_heads % c->kv_heads == 0 && q_heads / c->kv_heads <= 16,
+             "rb_attention_decode_static: %d query heads over %d KV heads unsupported", q_heads, c->kv_heads);
+  RB_REQUIRE(ctx->device >= 0 && ctx->device < 64, "rb_attention_decode_static: device index %d out of range", ctx->device);
+  int max_len = 0;
+  for (int b = 0; b < batch; ++b) {
+    RB_REQUIRE(c->host_lens[b] >= 1, "rb_attention_decode_static: sequence %d is empty", b);
+    max_len = std::max(max_len, c->host_lens[b]);
+  }
+  // One-time set-up per device, done by the first call on it: turn the symbol into a device address.
+  if (!g_static_attn_scratch_dev[ctx->device]) {
+    int current = -1;
+    RB_CUDA(cudaGetDevice(&current));
+    RB_REQUIRE(current == ctx->device, "rb_attention_decode_static: device %d must be current (it is %d)", ctx->device, current);
+    float* ptr = nullptr;
+    RB_CUDA(cudaGetSymbolAddress((void**)&ptr, g_static_attn_scratch));
+    g_static_attn_scratch_dev[ctx->device] = ptr;
+  }
+  float* scratch = g_static_attn_scratch_dev[ctx->device];
+  AParams p{};
+  const size_t loff = (size_t)layer * c->layer_stride_elems();
+  p.q = (const bf16*)q;
+  p.k = (const bf16*)c->k + loff;
+  p.v = (const bf16*)c->v + loff;
+  p.block_table = c->block_table;
+  p.seq_lens = c->seq_lens;
+  p.pages_per_seq = c->pages_per_seq;
+  p.s_new = 1;
+  p.q_heads = q_heads;
+  p.kv_heads = c->kv_heads;
+  p.group = q_heads / c->kv_heads;
+  p.scale_log2 = scale * kLog2e;
+  p.out = (bf16*)out;
+  switch (c->head_dim) {
+    case 64: return launch_attention_decode_static<64>(ctx, p, batch, max_len, scratch);
+    case 80: return launch_attention_decode_static<80>(ctx, p, batch, max_len, scratch);
+    case 96: return launch_attention_decode_static<96>(ctx, p, batch, max_len, scratch);
+    case 128: return launch_attention_decode_static<128>(ctx, p, batch, max_len, scratch);
+    case 256: return launch_attention_decode_static<256>(ctx, p, batch, max_len, scratch);
+  }
+  return fail(RB_ERR_UNIMPLEMENTED, "rb_attention_decode_static: head_dim %d has no kernel (64, 80, 96, 128, 256)", c->head_dim);
+}
