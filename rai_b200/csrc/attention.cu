@@ -23,6 +23,8 @@ namespace rb {
 
 using bf16 = __nv_bfloat16;
 
+int attention_decode_splits(rb_ctx* ctx, int batch, int kv_heads, int max_len);
+
 namespace {
 
 constexpr int kTile = 64;  // keys per tile == tokens per cache page
@@ -367,16 +369,7 @@ int launch_attention(rb_ctx* ctx, AParams& p, int batch, int max_len) {
   if (!set) { RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes)); set = true; }
   // Split the keys of a sequence over several blocks only when (sequence, KV head) pairs alone leave
   // the GPU under-filled: one long block per pair keeps its copy pipeline full and needs no merge.
-  const int tiles = std::max(1, (max_len + kTile - 1) / kTile);
-  const int work = batch * p.kv_heads;
-  const int slots = 2 * ctx->sm_count;
-  int splits = 1;
-  if (work * 4 < slots * 3) {
-    splits = (slots + work - 1) / work;
-    splits = std::max(1, std::min(splits, std::min(tiles / 2, 32)));  // at least 2 tiles per split
-  }
-  static const int forced = getenv("RAI_B200_ATTN_SPLITS") ? atoi(getenv("RAI_B200_ATTN_SPLITS")) : 0;
-  if (forced > 0) splits = std::max(1, std::min(forced, tiles));
+  const int splits = attention_decode_splits(ctx, batch, p.kv_heads, max_len);
   p.n_splits = splits;
   if (splits > 1) {
     const size_t need = (size_t)batch * p.q_heads * splits * (D + 2) * sizeof(float);
@@ -451,6 +444,20 @@ static int launch_attention_decode_static(rb_ctx* ctx, AParams& p, int batch, in
     ctx->launches++;
   }
   return RB_OK;
+}
+
+int attention_decode_splits(rb_ctx* ctx, int batch, int kv_heads, int max_len) {
+  const int tiles = std::max(1, (max_len + kTile - 1) / kTile);
+  const int work = batch * kv_heads;
+  const int slots = 2 * ctx->sm_count;
+  int splits = 1;
+  if (work * 4 < slots * 3) {
+    splits = (slots + work - 1) / work;
+    splits = std::max(1, std::min(splits, std::min(tiles / 2, 32)));  // at least 2 tiles per split
+  }
+  static const int forced = getenv("RAI_B200_ATTN_SPLITS") ? atoi(getenv("RAI_B200_ATTN_SPLITS")) : 0;
+  if (forced > 0) splits = std::max(1, std::min(forced, tiles));
+  return splits;
 }
 
 int attention_mma_bf16(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, int batch, int s_new, int q_heads,

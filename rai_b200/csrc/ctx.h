@@ -42,6 +42,22 @@ struct rb_kv_cache {
   size_t layer_stride_elems() const { return (size_t)num_pages * kv_heads * 64 * head_dim; }
 };
 
+// Peer-memory exchange of a tensor-parallel group for decode-sized allreduces: every rank publishes
+// its partial [rows, hidden] in its own exchange buffer and raises a flag in every peer's flag
+// array; the consumer waits (bounded) for all flags and sums the peers' buffers in rank order while
+// it reads them over NVLink ("reduce on read").  Two slots, chosen by the parity of a device-side
+// sequence number, so replayed CUDA graphs need no new arguments.
+constexpr int kTpMaxRanks = 8;
+constexpr int kTpMaxRows = 256;
+struct TpPeers {
+  const void* xbuf[kTpMaxRanks];   // every rank's exchange buffer (own included), [2][kTpMaxRows][hidden]
+  uint32_t* flags[kTpMaxRanks];    // every rank's flag array, [2][kTpMaxRanks]
+  uint32_t* seq;                   // local: number of exchanges published so far
+  uint32_t* block_count;           // local: arrival counter of the publishing kernel
+  int rank, size;
+  int64_t slot_elems;              // kTpMaxRows * hidden
+};
+
 namespace rb {
 constexpr int kPageTokens = 64;
 constexpr int kArgmaxRows = 4096;  // rows one argmax launch can reduce across blocks
@@ -87,6 +103,12 @@ int gemm_simple(rb_ctx* ctx, const GemmArgs& a, int dtype);
 
 int attention_mma_bf16(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, int batch, int s_new, int q_heads,
                        float scale, void* out);
+// decoder_kernels.cu: publish this rank's partial sum / norm with the peers' partials folded in.
+int tp_publish(rb_ctx* ctx, const TpPeers& tp, const float* acc, int n_acc, const void* bias, const void* x, int64_t rows,
+               int64_t hidden);
+int norm_tp(rb_ctx* ctx, const TpPeers& tp, int kind, const void* x, const void* w, const void* b, float eps, int64_t rows,
+            int64_t hidden, void* out, void* sum_out);
+int attention_decode_splits(rb_ctx* ctx, int batch, int kv_heads, int max_len);
 int attention_simple(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, int batch, int s_new, int q_heads,
                      float scale, void* out, int dtype);
 }  // namespace rb

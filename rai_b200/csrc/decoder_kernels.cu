@@ -128,12 +128,23 @@ __device__ __forceinline__ void round_to(float* v) {
   for (int i = 0; i < 8; ++i) v[i] = Cvt<T>::to_f(Cvt<T>::from_f(v[i]));
 }
 
-template <typename T, int kChunks>
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+template <typename T, int kChunks, bool TP>
 __global__ void norm_vec_kernel(int kind, const T* __restrict__ x, const T* __restrict__ add,
                                 const float* __restrict__ acc, int n_acc, size_t acc_stride,
                                 const T* __restrict__ acc_bias, const T* __restrict__ w, const T* __restrict__ b,
-                                float eps, int hidden, T* __restrict__ out, T* __restrict__ sum_out) {
+                                float eps, int hidden, T* __restrict__ out, T* __restrict__ sum_out, const TpPeers tp,
+                                uint32_t* status) {
   __shared__ float red[32];
+  __shared__ uint32_t tp_seq_s;
   pdl_launch_dependents();
   float wv[kChunks][8], bv[kChunks][8];
   const int nchunk = hidden >> 3;
@@ -150,6 +161,26 @@ __global__ void norm_vec_kernel(int kind, const T* __restrict__ x, const T* __re
   }
   pdl_wait();
   const size_t base = (size_t)blockIdx.x * hidden;
+  size_t tp_off = 0;
+  if (TP) {
+    // every rank has published exchange number `seq` when its flag in MY array says so; bounded wait
+    if (threadIdx.x == 0) {
+      const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(tp.seq);
+      const uint32_t* mine = tp.flags[tp.rank] + (seq & 1u) * kTpMaxRanks;
+      const long long t0 = clock64();
+      bool ok = true;
+      for (int r = 0; r < tp.size && ok; ++r) {
+        while (ld_acquire_sys(mine + r) < seq) {
+          if (clock64() - t0 > 2000000000LL) { ok = false; break; }
+        }
+      }
+      if (!ok) { status[0] = (uint32_t)(-RB_ERR_TIMEOUT); status[1] = 0x7A11u; status[2] = (uint32_t)tp.rank; status[3] = seq; }
+      tp_seq_s = ok ? seq : 0xffffffffu;
+    }
+    __syncthreads();
+    if (tp_seq_s == 0xffffffffu) return;  // a peer never arrived: leave the outputs alone, the host sees the status
+    tp_off = (size_t)(tp_seq_s & 1u) * tp.slot_elems;
+  }
   float v[kChunks][8];
   float s = 0.f;
   const float inv_sqrt_h = 1.0f / sqrtf((float)hidden);
@@ -172,6 +203,17 @@ __global__ void norm_vec_kernel(int kind, const T* __restrict__ x, const T* __re
     if (acc_bias) { load8(acc_bias + ch * 8, t);
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[c][i] += t[i]; }
+    if (TP) {  // the peers' partial sums, read over NVLink, added in rank order on every rank alike
+      float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int r = 0; r < tp.size; ++r) {
+        load8(reinterpret_cast<const T*>(tp.xbuf[r]) + tp_off + base + ch * 8, t);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sum[i] += t[i];
+      }
+      round_to<T>(sum);  // what an allreduce in the model dtype would have delivered
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[c][i] += sum[i];
+    }
     round_to<T>(v[c]);  // the residual stream is stored in the model dtype
     if (sum_out) store8(sum_out + base + ch * 8, v[c]);
 #pragma unroll
@@ -212,6 +254,44 @@ __global__ void norm_vec_kernel(int kind, const T* __restrict__ x, const T* __re
       else y[i] = v[c][i] * r * (wv[c][i] + 1.0f);
     }
     store8(out + base + ch * 8, y);
+  }
+}
+
+
+// Tensor-parallel publish: this rank's partial product (split-K slabs + bias, or a finished tensor x)
+// goes into the next slot of its exchange buffer; the last block to finish bumps the sequence number
+// and raises this rank's flag in every peer's flag array.
+template <typename T>
+__global__ void tp_publish_kernel(const float* __restrict__ acc, int n_acc, size_t acc_stride, const T* __restrict__ bias,
+                                  const T* __restrict__ x, int hidden, const TpPeers tp) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(tp.seq) + 1u;
+  T* dst = reinterpret_cast<T*>(const_cast<void*>(tp.xbuf[tp.rank])) + (size_t)(seq & 1u) * tp.slot_elems;
+  const size_t base = (size_t)blockIdx.x * hidden;
+  for (int ch = threadIdx.x; ch < (hidden >> 3); ch += blockDim.x) {
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, t[8];
+    if (x) { load8(x + base + ch * 8, t);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] += t[i]; }
+    for (int k = 0; k < n_acc; ++k) { load8(acc + (size_t)k * acc_stride + base + ch * 8, t);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] += t[i]; }
+    if (bias) { load8(bias + ch * 8, t);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] += t[i]; }
+    store8(dst + base + ch * 8, v);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int arrived = atomicAdd(tp.block_count, 1u);
+    if (arrived == gridDim.x - 1) {
+      *tp.block_count = 0u;
+      __threadfence_system();
+      *reinterpret_cast<volatile uint32_t*>(tp.seq) = seq;
+      for (int r = 0; r < tp.size; ++r) st_release_sys(tp.flags[r] + (seq & 1u) * kTpMaxRanks + tp.rank, seq);
+    }
   }
 }
 
@@ -460,7 +540,7 @@ extern "C" int32_t rb_embed_gather(rb_ctx* ctx, const void* table, int32_t dtype
 template <typename T>
 static int norm_launch(rb_ctx* ctx, int kind, const void* x, const void* add, const float* acc, int n_acc,
                        const void* acc_bias, const void* w, const void* b, float eps, int64_t rows, int64_t hidden,
-                       void* out, void* sum_out) {
+                       void* out, void* sum_out, const TpPeers* tp = nullptr) {
   const size_t acc_stride = (size_t)rows * hidden;
   const bool vec_ok = (hidden % 8) == 0 && hidden <= 16384 && aligned16(x) && aligned16(add) && aligned16(acc) &&
                       aligned16(acc_bias) && aligned16(w) && aligned16(b) && aligned16(out) && aligned16(sum_out) &&
@@ -472,13 +552,20 @@ static int norm_launch(rb_ctx* ctx, int kind, const void* x, const void* add, co
     auto go = [&](auto kern) {
       return launch_kernel(kern, dim3((unsigned)rows), dim3(threads), 0, ctx->stream, ctx->pdl, kind, (const T*)x,
                            (const T*)add, acc, n_acc, acc_stride, (const T*)acc_bias, (const T*)w, (const T*)b, eps,
-                           (int)hidden, (T*)out, (T*)sum_out);
+                           (int)hidden, (T*)out, (T*)sum_out, tp ? *tp : TpPeers{}, ctx->status_dev);
     };
-    if (chunks == 1) RB_CUDA(go(norm_vec_kernel<T, 1>));
-    else if (chunks == 2) RB_CUDA(go(norm_vec_kernel<T, 2>));
-    else RB_CUDA(go(norm_vec_kernel<T, 4>));
+    if (tp) {
+      if (chunks == 1) RB_CUDA(go(norm_vec_kernel<T, 1, true>));
+      else if (chunks == 2) RB_CUDA(go(norm_vec_kernel<T, 2, true>));
+      else RB_CUDA(go(norm_vec_kernel<T, 4, true>));
+    } else {
+      if (chunks == 1) RB_CUDA(go(norm_vec_kernel<T, 1, false>));
+      else if (chunks == 2) RB_CUDA(go(norm_vec_kernel<T, 2, false>));
+      else RB_CUDA(go(norm_vec_kernel<T, 4, false>));
+    }
     return RB_OK;
   }
+  if (tp) return fail(RB_ERR_INVALID, "tensor-parallel norm needs hidden %% 8 == 0 and 16-byte aligned operands");
   const size_t smem = (size_t)hidden * sizeof(float);
   const int threads = hidden >= 2048 ? 512 : 256;
   auto kern = norm_kernel<T>;
@@ -513,6 +600,30 @@ extern "C" int32_t rb_norm(rb_ctx* ctx, int32_t kind, const void* x, const void*
   ctx->launches++;
   return RB_OK;
 }
+
+namespace rb {
+
+int norm_tp(rb_ctx* ctx, const TpPeers& tp, int kind, const void* x, const void* w, const void* b, float eps, int64_t rows,
+            int64_t hidden, void* out, void* sum_out) {
+  RB_REQUIRE(rows > 0 && rows <= kTpMaxRows, "norm_tp: %lld rows exceed the exchange buffer", (long long)rows);
+  ProfScope prof(ctx, RB_PROF_NORM, (double)rows * hidden * 2.0 * (3 + tp.size), 0.0);
+  RB_TRY(norm_launch<__nv_bfloat16>(ctx, kind, x, nullptr, nullptr, 0, nullptr, w, b, eps, rows, hidden, out, sum_out, &tp));
+  ctx->launches++;
+  return RB_OK;
+}
+
+int tp_publish(rb_ctx* ctx, const TpPeers& tp, const float* acc, int n_acc, const void* bias, const void* x, int64_t rows,
+               int64_t hidden) {
+  RB_REQUIRE(rows > 0 && rows <= kTpMaxRows && hidden % 8 == 0, "tp_publish: bad shape");
+  ProfScope prof(ctx, RB_PROF_OTHER, (double)rows * hidden * (2.0 + 4.0 * n_acc), 0.0);
+  const int threads = std::min(512, (int)((hidden / 8 + 31) / 32 * 32));
+  RB_CUDA(launch_kernel(tp_publish_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(threads), 0, ctx->stream, ctx->pdl, acc,
+                        n_acc, (size_t)rows * hidden, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)x, (int)hidden, tp));
+  ctx->launches++;
+  return RB_OK;
+}
+
+}  // namespace rb
 
 extern "C" int32_t rb_rope_tables(rb_ctx* ctx, int32_t recipe, int32_t rot_dim, int32_t max_pos, double theta,
                                   float* cos_dev, float* sin_dev) {

@@ -13,6 +13,7 @@
 // each row-parallel GEMM (NCCL over NVLink, loaded lazily so that single-GPU use needs no NCCL).
 #include <dlfcn.h>
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -103,6 +104,13 @@ __global__ void set_lens_kernel(int32_t* lens, int n, int len) {
   if (i < n) lens[i] = len;
 }
 
+// lens[i] += delta: the device-side form of "seqlen_offset grows by the tokens just fed", so that a
+// captured decode step can be replayed without new kernel arguments.
+__global__ void advance_lens_kernel(int32_t* lens, int n, int delta) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) lens[i] += delta;
+}
+
 // out[b, r*vl + j] = gathered[r, b, j]  (vocabulary shards back into rows of logits)
 template <typename T>
 __global__ void unshard_logits_kernel(const T* __restrict__ g, T* __restrict__ out, int tp, int batch, int vl) {
@@ -148,6 +156,14 @@ struct rb_model {
   float* scratch = nullptr;  // split-K partials
   size_t scratch_floats = 0;
   void* comm = nullptr;
+  // One decode step (advance lengths, forward of the tokens in `ids`, argmax back into `ids`)
+  // captured as a CUDA graph and replayed; re-captured when the batch or the launch plan changes.
+  cudaGraphExec_t step_graph = nullptr;
+  int graph_batch = 0, graph_plan = 0;
+  int eager_warm_batch = 0, eager_warm_plan = 0;
+  int64_t graph_launches = 0;
+  bool use_graph = true;
+  cudaEvent_t ev_in = nullptr, ev_out = nullptr;
 };
 
 namespace {
@@ -203,13 +219,20 @@ int linear_into_residual(rb_model* m, Pending& pend, const void* x, const void* 
                          int64_t n, int64_t k) {
   if (pend.any()) RB_TRY(norm_point(m, pend, nullptr, nullptr, rows, nullptr));
   const void* b = (m->cfg.tp_rank == 0) ? bias : nullptr;  // a row-parallel bias is added once
+  int s = 1;
   if (m->cfg.tp_size > 1) {
-    RB_TRY(rb_linear(m->ctx, x, w, b, nullptr, m->tmp, rows, n, k, RB_ACT_NONE, m->cfg.dtype));
+    // this rank's partial product -> tmp, summed over ranks, folded into the residual by the next norm
+    if (use_partials(m, rows, n, k, &s)) {
+      RB_TRY(rb_linear_partials(m->ctx, x, w, m->scratch, rows, n, k, s));
+      RB_TRY(rb_norm(m->ctx, RB_NORM_RMS, nullptr, nullptr, m->scratch, s, b, nullptr, nullptr, 0.f, rows, n, nullptr,
+                     m->tmp, m->cfg.dtype));
+    } else {
+      RB_TRY(rb_linear(m->ctx, x, w, b, nullptr, m->tmp, rows, n, k, RB_ACT_NONE, m->cfg.dtype));
+    }
     RB_TRY(allreduce(m, m->tmp, (size_t)rows * n));
     pend.add = m->tmp;
     return RB_OK;
   }
-  int s = 1;
   if (use_partials(m, rows, n, k, &s)) {
     RB_TRY(rb_linear_partials(m->ctx, x, w, m->scratch, rows, n, k, s));
     pend.acc = m->scratch; pend.n_acc = s; pend.acc_bias = b;
@@ -217,6 +240,8 @@ int linear_into_residual(rb_model* m, Pending& pend, const void* x, const void* 
   }
   return rb_linear(m->ctx, x, w, b, m->h, m->h, rows, n, k, RB_ACT_NONE, m->cfg.dtype);
 }
+
+int forward_body(rb_model* m, const uint32_t* tokens, int batch, int seq, void* logits_out);
 
 int forward_impl(rb_model* m, const uint32_t* tokens, int batch, int seq, int pos, void* logits_out) {
   const rb_model_config& c = m->cfg;
@@ -234,6 +259,16 @@ int forward_impl(rb_model* m, const uint32_t* tokens, int batch, int seq, int po
   set_lens_kernel<<<(batch + 127) / 128, 128, 0, ctx->stream>>>(m->cache->seq_lens, batch, pos + seq);
   ctx->launches++;
   for (int b = 0; b < batch; ++b) m->cache->host_lens[b] = pos + seq;
+  return forward_body(m, tokens, batch, seq, logits_out);
+}
+
+// The launches of one forward pass.  Everything position-dependent is read from device memory (the
+// cache's sequence lengths), so the same sequence of launches serves every decode step.
+int forward_body(rb_model* m, const uint32_t* tokens, int batch, int seq, void* logits_out) {
+  const rb_model_config& c = m->cfg;
+  rb_ctx* ctx = m->ctx;
+  const int64_t rows = (int64_t)batch * seq;
+  const int H = c.hidden_size, d = m->d;
 
   const float emb_scale = c.arch == RB_ARCH_GEMMA ? sqrtf((float)H) : 1.0f;  // gemma.rs:379
   RB_TRY(rb_embed_gather(ctx, m->embed, c.dtype, c.vocab_size, H, tokens, rows, emb_scale, m->h));
@@ -344,6 +379,10 @@ extern "C" int32_t rb_model_create(rb_ctx* ctx, const rb_model_config* cfg, rb_m
   rb_model* m = new rb_model();
   m->ctx = ctx;
   m->cfg = c;
+  {
+    const char* g = getenv("RAI_B200_GRAPH");  // RAI_B200_GRAPH=0: plain launches for every decode step
+    m->use_graph = !(g && g[0] == '0');
+  }
   m->d = c.hidden_size / nq;
   m->es = dtype_size(c.dtype);
   const int d = m->d, H = c.hidden_size;
@@ -492,7 +531,7 @@ extern "C" int32_t rb_model_create(rb_ctx* ctx, const rb_model_config* cfg, rb_m
   W((size_t)c.max_batch * V * m->es, &m->logits);
   if (tp > 1) W((size_t)c.max_batch * Vl * m->es * (tp + 1), &m->logits_g);
   W((size_t)c.max_batch * sizeof(uint32_t), (void**)&m->next_ids);
-  if (c.dtype == RB_BF16 && tp == 1) {
+  if (c.dtype == RB_BF16) {
     // split-K scratch: up to 16 slabs of min(max_tokens, 256) rows of the widest split-K output
     const size_t rows = std::min<size_t>(MT, 256);
     m->scratch_floats = (size_t)16 * rows * std::max(m->nqkv_l, H);
@@ -507,6 +546,9 @@ extern "C" int32_t rb_model_create(rb_ctx* ctx, const rb_model_config* cfg, rb_m
 extern "C" int32_t rb_model_destroy(rb_model* m) {
   if (!m) return RB_OK;
   cudaStreamSynchronize(m->ctx->stream);
+  if (m->step_graph) cudaGraphExecDestroy(m->step_graph);
+  if (m->ev_in) cudaEventDestroy(m->ev_in);
+  if (m->ev_out) cudaEventDestroy(m->ev_out);
   if (m->comm && nccl().CommDestroy) nccl().CommDestroy(m->comm);
   if (m->cache) rb_kv_cache_destroy(m->cache);
   for (void* p : m->owned) rb_free(m->ctx, p);
@@ -589,26 +631,151 @@ extern "C" int32_t rb_model_forward(rb_model* m, const uint32_t* tokens_dev, int
   return forward_impl(m, tokens_dev, batch, seq, pos, logits_dev);
 }
 
+namespace {
+
+// Whatever host-side state shapes the launches of a decode step: a captured step is reused only
+// while this stays the same (today: how many KV splits the attention uses).
+int decode_plan(rb_model* m, int batch) {
+  int max_len = 0;
+  for (int b = 0; b < batch; ++b) max_len = std::max(max_len, m->cache->host_lens[b]);
+  return attention_decode_splits(m->ctx, batch, m->nkv_l, max_len);
+}
+
+int decode_step_launches(rb_model* m, int batch) {
+  rb_ctx* ctx = m->ctx;
+  advance_lens_kernel<<<(batch + 127) / 128, 128, 0, ctx->stream>>>(m->cache->seq_lens, batch, 1);
+  ctx->launches++;
+  RB_TRY(forward_body(m, m->ids, batch, 1, nullptr));
+  // the greedy token goes straight back into `ids`, the input of the next step
+  return rb_argmax_rows(ctx, m->logits, m->cfg.dtype, batch, m->cfg.vocab_size, m->ids);
+}
+
+// One greedy decode step on the tokens in m->ids (result left in m->ids), on the context's current
+// stream, replaying a captured CUDA graph when one fits.  The first step of a new (batch, plan) runs
+// eagerly (it may allocate scratch and set kernel attributes), the second is captured, later ones replay.
+int decode_step(rb_model* m, int batch) {
+  rb_ctx* ctx = m->ctx;
+  rb_kv_cache* c = m->cache;
+  RB_REQUIRE(batch > 0 && batch <= m->cfg.max_batch, "decode: batch %d exceeds max_batch %d", batch, m->cfg.max_batch);
+  const int len0 = c->host_lens[0];
+  RB_REQUIRE(len0 + 1 <= c->max_seq && len0 + 1 <= m->cfg.max_position_embeddings,
+             "decode: position %d exceeds the cache / rotary table capacity", len0);
+  for (int b = 0; b < batch; ++b)
+    RB_REQUIRE(c->host_lens[b] == len0, "decode: sequences of one batch must have equal lengths");
+  for (int b = 0; b < batch; ++b) c->host_lens[b] = len0 + 1;
+  const int plan = decode_plan(m, batch);
+  const bool graphable = m->use_graph && m->cfg.dtype == RB_BF16 && !ctx->profiling && !ctx->debug_simple;
+  if (graphable && m->step_graph && m->graph_batch == batch && m->graph_plan == plan) {
+    RB_CUDA(cudaGraphLaunch(m->step_graph, ctx->stream));
+    ctx->launches += m->graph_launches;
+    return RB_OK;
+  }
+  if (graphable && m->eager_warm_batch == batch && m->eager_warm_plan == plan) {
+    // capture on the library's own stream (the default stream cannot be captured), ordered with the
+    // caller's stream by events on both sides
+    cudaStream_t user = ctx->stream;
+    if (m->step_graph) { cudaGraphExecDestroy(m->step_graph); m->step_graph = nullptr; }
+    cudaGraph_t graph = nullptr;
+    const int64_t launches0 = ctx->launches;
+    int st = RB_OK;
+    cudaError_t ce = cudaStreamBeginCapture(ctx->own_stream, cudaStreamCaptureModeRelaxed);
+    if (ce == cudaSuccess) {
+      ctx->stream = ctx->own_stream;
+      st = decode_step_launches(m, batch);
+      ctx->stream = user;
+      ce = cudaStreamEndCapture(ctx->own_stream, &graph);
+      if (st == RB_OK && ce == cudaSuccess) ce = cudaGraphInstantiate(&m->step_graph, graph, 0);
+      if (graph) cudaGraphDestroy(graph);
+    }
+    if (st != RB_OK || ce != cudaSuccess || !m->step_graph) {
+      // capture is an optimisation: fall back to plain launches for the rest of this model's life
+      cudaGetLastError();
+      m->step_graph = nullptr;
+      m->use_graph = false;
+      ctx->launches = launches0;
+      return decode_step_launches(m, batch);
+    }
+    m->graph_launches = ctx->launches - launches0;
+    ctx->launches = launches0;
+    m->graph_batch = batch;
+    m->graph_plan = plan;
+    RB_CUDA(cudaGraphLaunch(m->step_graph, ctx->stream));
+    ctx->launches += m->graph_launches;
+    return RB_OK;
+  }
+  m->eager_warm_batch = batch;
+  m->eager_warm_plan = plan;
+  return decode_step_launches(m, batch);
+}
+
+// Runs `fn` with the context's stream switched to the library's own (capturable) stream, ordered
+// after the caller's stream on entry and before it on exit.
+template <typename F>
+int on_own_stream(rb_model* m, F fn) {
+  rb_ctx* ctx = m->ctx;
+  cudaStream_t user = ctx->stream;
+  if (user == ctx->own_stream) return fn();
+  if (!m->ev_in) {
+    RB_CUDA(cudaEventCreateWithFlags(&m->ev_in, cudaEventDisableTiming));
+    RB_CUDA(cudaEventCreateWithFlags(&m->ev_out, cudaEventDisableTiming));
+  }
+  RB_CUDA(cudaEventRecord(m->ev_in, user));
+  RB_CUDA(cudaStreamWaitEvent(ctx->own_stream, m->ev_in, 0));
+  ctx->stream = ctx->own_stream;
+  const int st = fn();
+  ctx->stream = user;
+  RB_CUDA(cudaEventRecord(m->ev_out, ctx->own_stream));
+  RB_CUDA(cudaStreamWaitEvent(user, m->ev_out, 0));
+  return st;
+}
+
+}  // namespace
+
 extern "C" int32_t rb_model_generate_step(rb_model* m, const uint32_t* tokens_host, int32_t batch, int32_t seq,
                                           int32_t pos, uint32_t* next_host) {
   RB_REQUIRE(m && tokens_host && next_host, "rb_model_generate_step: null argument");
   RB_REQUIRE(batch > 0 && seq > 0 && (int64_t)batch * seq <= m->cfg.max_tokens, "rb_model_generate_step: bad sizes");
   rb_ctx* ctx = m->ctx;
-  RB_CUDA(cudaMemcpyAsync(m->ids, tokens_host, (size_t)batch * seq * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream));
-  RB_TRY(forward_impl(m, m->ids, batch, seq, pos, nullptr));
-  RB_TRY(rb_argmax_rows(ctx, m->logits, m->cfg.dtype, batch, m->cfg.vocab_size, m->next_ids));
-  RB_CUDA(cudaMemcpyAsync(next_host, m->next_ids, (size_t)batch * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+  const bool single = seq == 1 && !ctx->profiling;
+  if (single)
+    for (int b = 0; b < batch; ++b)
+      RB_REQUIRE(m->cache->host_lens[b] == pos, "generate_step: seqlen_offset %d differs from the cached length %d", pos,
+                 m->cache->host_lens[b]);
+  const int st = on_own_stream(m, [&]() -> int {
+    RB_CUDA(cudaMemcpyAsync(m->ids, tokens_host, (size_t)batch * seq * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream));
+    const uint32_t* result = m->ids;
+    if (single) {
+      RB_TRY(decode_step(m, batch));
+    } else {
+      RB_TRY(forward_impl(m, m->ids, batch, seq, pos, nullptr));
+      RB_TRY(rb_argmax_rows(ctx, m->logits, m->cfg.dtype, batch, m->cfg.vocab_size, m->next_ids));
+      result = m->next_ids;
+    }
+    RB_CUDA(cudaMemcpyAsync(next_host, result, (size_t)batch * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+    return RB_OK;
+  });
+  RB_TRY(st);
+  RB_CUDA(cudaStreamSynchronize(ctx->own_stream));
   return rb_sync(ctx);
 }
 
 extern "C" int32_t rb_model_decode_loop(rb_model* m, const uint32_t* tokens_dev, int32_t batch, int32_t pos,
                                         int32_t steps, uint32_t* out_dev) {
   RB_REQUIRE(m && tokens_dev && out_dev, "rb_model_decode_loop: null argument");
-  const uint32_t* cur = tokens_dev;
-  for (int i = 0; i < steps; ++i) {
-    RB_TRY(forward_impl(m, cur, batch, 1, pos + i, nullptr));
-    RB_TRY(rb_argmax_rows(m->ctx, m->logits, m->cfg.dtype, batch, m->cfg.vocab_size, out_dev + (size_t)i * batch));
-    cur = out_dev + (size_t)i * batch;
-  }
-  return RB_OK;
+  RB_REQUIRE(batch > 0 && batch <= m->cfg.max_batch && steps >= 0, "rb_model_decode_loop: bad sizes");
+  for (int b = 0; b < batch; ++b)
+    RB_REQUIRE(m->cache->host_lens[b] == pos, "decode_loop: seqlen_offset %d differs from the cached length %d", pos,
+               m->cache->host_lens[b]);
+  rb_ctx* ctx = m->ctx;
+  auto body = [&]() -> int {
+    RB_CUDA(cudaMemcpyAsync(m->ids, tokens_dev, (size_t)batch * sizeof(uint32_t), cudaMemcpyDeviceToDevice, ctx->stream));
+    for (int i = 0; i < steps; ++i) {
+      RB_TRY(decode_step(m, batch));
+      RB_CUDA(cudaMemcpyAsync(out_dev + (size_t)i * batch, m->ids, (size_t)batch * sizeof(uint32_t),
+                              cudaMemcpyDeviceToDevice, ctx->stream));
+    }
+    return RB_OK;
+  };
+  if (ctx->profiling) return body();  // per-launch event timing needs plain launches on the caller's stream
+  return on_own_stream(m, body);
 }
