@@ -264,6 +264,7 @@ __global__ void norm_vec_kernel(int kind, const T* __restrict__ x, const T* __re
 template <typename T>
 __global__ void tp_publish_kernel(const float* __restrict__ acc, int n_acc, size_t acc_stride, const T* __restrict__ bias,
                                   const T* __restrict__ x, int hidden, const TpPeers tp) {
+  __shared__ uint32_t last_block;
   pdl_launch_dependents();
   pdl_wait();
   const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(tp.seq) + 1u;
@@ -282,17 +283,20 @@ __global__ void tp_publish_kernel(const float* __restrict__ acc, int n_acc, size
       for (int i = 0; i < 8; ++i) v[i] += t[i]; }
     store8(dst + base + ch * 8, v);
   }
-  __threadfence_system();
-  __syncthreads();
+  __syncthreads();  // the block's stores are ordered before thread 0's fence (cumulativity through the barrier)
   if (threadIdx.x == 0) {
+    __threadfence();
     const unsigned int arrived = atomicAdd(tp.block_count, 1u);
-    if (arrived == gridDim.x - 1) {
+    last_block = (arrived == gridDim.x - 1) ? 1u : 0u;
+    if (last_block) {
       *tp.block_count = 0u;
-      __threadfence_system();
       *reinterpret_cast<volatile uint32_t*>(tp.seq) = seq;
-      for (int r = 0; r < tp.size; ++r) st_release_sys(tp.flags[r] + (seq & 1u) * kTpMaxRanks + tp.rank, seq);
+      __threadfence_system();  // one system-scope fence, then plain flag stores to all peers in parallel
     }
   }
+  __syncthreads();
+  if (last_block && threadIdx.x < tp.size)
+    *reinterpret_cast<volatile uint32_t*>(tp.flags[threadIdx.x] + (seq & 1u) * kTpMaxRanks + tp.rank) = seq;
 }
 
 // ------------------------------------------------------------------------------------------

@@ -128,7 +128,8 @@ struct Pending {  // terms still to be added to the residual stream
   int n_acc = 0;
   const void* acc_bias = nullptr;
   const void* add = nullptr;
-  bool any() const { return (acc && n_acc > 0) || add; }
+  bool exchange = false;  // the term sits in the peers' exchange buffers (tensor parallel, decode-sized)
+  bool any() const { return (acc && n_acc > 0) || add || exchange; }
 };
 
 }  // namespace
@@ -156,6 +157,11 @@ struct rb_model {
   float* scratch = nullptr;  // split-K partials
   size_t scratch_floats = 0;
   void* comm = nullptr;
+  // peer-memory exchange for decode-sized allreduces (see TpPeers); xchg_base is this rank's region
+  TpPeers peers{};
+  void* xchg_base = nullptr;
+  void* peer_base[kTpMaxRanks] = {};
+  bool use_exchange = false;
   // One decode step (advance lengths, forward of the tokens in `ids`, argmax back into `ids`)
   // captured as a CUDA graph and replayed; re-captured when the batch or the launch plan changes.
   cudaGraphExec_t step_graph = nullptr;
@@ -200,6 +206,11 @@ int allreduce(rb_model* m, void* buf, size_t count) {
 // v = h + pending ; h = v ; out = norm(v)   (out may be NULL: only fold the pending terms)
 int norm_point(rb_model* m, Pending& pend, const void* w, const void* b, int64_t rows, void* out) {
   if (!out && !pend.any()) return RB_OK;
+  if (pend.exchange) {
+    RB_TRY(norm_tp(m->ctx, m->peers, norm_kind(m), m->h, w, b, (float)m->cfg.norm_eps, rows, m->cfg.hidden_size, out, m->h));
+    pend = Pending();
+    return RB_OK;
+  }
   RB_TRY(rb_norm(m->ctx, norm_kind(m), m->h, pend.add, pend.acc, pend.n_acc, pend.acc_bias, w, b,
                  (float)m->cfg.norm_eps, rows, m->cfg.hidden_size, out, pend.any() ? m->h : nullptr, m->cfg.dtype));
   pend = Pending();
@@ -222,6 +233,18 @@ int linear_into_residual(rb_model* m, Pending& pend, const void* x, const void* 
   int s = 1;
   if (m->cfg.tp_size > 1) {
     // this rank's partial product -> tmp, summed over ranks, folded into the residual by the next norm
+    if (m->use_exchange && rows <= kTpMaxRows && n == m->cfg.hidden_size) {
+      // decode-sized: publish into the exchange buffer; the next norm sums the peers' buffers as it reads
+      if (use_partials(m, rows, n, k, &s)) {
+        RB_TRY(rb_linear_partials(m->ctx, x, w, m->scratch, rows, n, k, s));
+        RB_TRY(tp_publish(m->ctx, m->peers, m->scratch, s, b, nullptr, rows, n));
+      } else {
+        RB_TRY(rb_linear(m->ctx, x, w, b, nullptr, m->tmp, rows, n, k, RB_ACT_NONE, m->cfg.dtype));
+        RB_TRY(tp_publish(m->ctx, m->peers, nullptr, 0, nullptr, m->tmp, rows, n));
+      }
+      pend.exchange = true;
+      return RB_OK;
+    }
     if (use_partials(m, rows, n, k, &s)) {
       RB_TRY(rb_linear_partials(m->ctx, x, w, m->scratch, rows, n, k, s));
       RB_TRY(rb_norm(m->ctx, RB_NORM_RMS, nullptr, nullptr, m->scratch, s, b, nullptr, nullptr, 0.f, rows, n, nullptr,
@@ -355,6 +378,53 @@ extern "C" int32_t rb_model_tp_init(rb_model* m, const void* id, int32_t id_byte
   memcpy(u.bytes, id, 128);
   RB_CUDA(cudaSetDevice(m->ctx->device));
   RB_NCCL(nccl().CommInitRank(&m->comm, m->cfg.tp_size, u, m->cfg.tp_rank));
+  const char* xe = getenv("RAI_B200_TP_EXCHANGE");  // RAI_B200_TP_EXCHANGE=0: NCCL allreduce for every size
+  if (m->cfg.dtype != RB_BF16 || m->cfg.tp_size > kTpMaxRanks || (xe && xe[0] == '0') || (m->cfg.hidden_size % 8)) return RB_OK;
+  // ---- peer-memory exchange: one region per rank = [flags 2 x 8 | seq | block_count | pad to 256 B | 2 slots]
+  rb_ctx* ctx = m->ctx;
+  const int tp = m->cfg.tp_size, rank = m->cfg.tp_rank;
+  const size_t slot_elems = (size_t)kTpMaxRows * m->cfg.hidden_size;
+  const size_t bytes = 256 + 2 * slot_elems * 2;
+  RB_TRY(rb_malloc(ctx, bytes, &m->xchg_base));
+  m->owned.push_back(m->xchg_base);
+  RB_CUDA(cudaMemsetAsync(m->xchg_base, 0, bytes, ctx->stream));
+  cudaIpcMemHandle_t mine;
+  RB_CUDA(cudaIpcGetMemHandle(&mine, m->xchg_base));
+  // all-gather the handles with NCCL itself (device staging), then open every peer's region
+  char* stage = nullptr;
+  RB_CUDA(cudaMalloc(&stage, sizeof(mine) * (size_t)(tp + 1)));
+  RB_CUDA(cudaMemcpyAsync(stage, &mine, sizeof(mine), cudaMemcpyHostToDevice, ctx->stream));
+  RB_NCCL(nccl().AllGather(stage, stage + sizeof(mine), sizeof(mine), kNcclUint8, m->comm, ctx->stream));
+  std::vector<cudaIpcMemHandle_t> all(tp);
+  RB_CUDA(cudaMemcpyAsync(all.data(), stage + sizeof(mine), sizeof(mine) * (size_t)tp, cudaMemcpyDeviceToHost, ctx->stream));
+  RB_CUDA(cudaStreamSynchronize(ctx->stream));
+  cudaFree(stage);
+  for (int r = 0; r < tp; ++r) {
+    if (r == rank) { m->peer_base[r] = m->xchg_base; continue; }
+    cudaError_t e = cudaIpcOpenMemHandle(&m->peer_base[r], all[r], cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {  // no peer access between these GPUs: stay on NCCL
+      cudaGetLastError();
+      for (int q = 0; q < r; ++q) if (q != rank && m->peer_base[q]) { cudaIpcCloseMemHandle(m->peer_base[q]); m->peer_base[q] = nullptr; }
+      return RB_OK;
+    }
+  }
+  TpPeers& p = m->peers;
+  for (int r = 0; r < tp; ++r) {
+    p.flags[r] = (uint32_t*)m->peer_base[r];
+    p.xbuf[r] = (const char*)m->peer_base[r] + 256;
+  }
+  // sequence number and arrival counter are touched by this GPU only: keep them off the line the peers write
+  void* local = nullptr;
+  RB_TRY(rb_malloc(ctx, 256, &local));
+  m->owned.push_back(local);
+  RB_CUDA(cudaMemsetAsync(local, 0, 256, ctx->stream));
+  p.seq = (uint32_t*)local;
+  p.block_count = p.seq + 32;
+  p.rank = rank; p.size = tp; p.slot_elems = (int64_t)slot_elems;
+  // nobody may publish before every rank has zeroed its region and opened its peers: meet once
+  RB_TRY(allreduce(m, m->tmp, 8));
+  RB_CUDA(cudaStreamSynchronize(ctx->stream));
+  m->use_exchange = true;
   return RB_OK;
 }
 
@@ -549,6 +619,8 @@ extern "C" int32_t rb_model_destroy(rb_model* m) {
   if (m->step_graph) cudaGraphExecDestroy(m->step_graph);
   if (m->ev_in) cudaEventDestroy(m->ev_in);
   if (m->ev_out) cudaEventDestroy(m->ev_out);
+  for (int r = 0; r < kTpMaxRanks; ++r)
+    if (m->peer_base[r] && m->peer_base[r] != m->xchg_base) cudaIpcCloseMemHandle(m->peer_base[r]);
   if (m->comm && nccl().CommDestroy) nccl().CommDestroy(m->comm);
   if (m->cache) rb_kv_cache_destroy(m->cache);
   for (void* p : m->owned) rb_free(m->ctx, p);

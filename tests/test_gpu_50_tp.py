@@ -1,4 +1,4 @@
-"""Tensor-parallel decoders on 2 (and 4) GPUs of one box against the CPU oracle.  Skipped on a
+"""Tensor-parallel decoders on 2, 4 and 8 GPUs of one box against the CPU oracle.  Skipped on a
 single-GPU box; the sharding arithmetic itself is covered on CPU ranks by tests/test_tp_plan.py."""
 import os
 import subprocess
@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_tensor_parallel_matches_oracle(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")

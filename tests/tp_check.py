@@ -37,8 +37,7 @@ def main():
         if cfg["intermediate_size"] % world or cfg["vocab_size"] % world:
             continue
         w = synth.weights(cfg, 31)
-        prompt = synth.prompt(cfg, 2, 40, 31)
-        m = Model(cfg, dtype, dev, 2, 128, tp_rank=rank, tp_size=world)
+        m = Model(cfg, dtype, dev, 2, 256, tp_rank=rank, tp_size=world)
         uid = [None]
         if rank == 0:
             buf = ctypes.create_string_buffer(128)
@@ -47,14 +46,20 @@ def main():
         dist.broadcast_object_list(uid, 0)
         m.tp_init(uid[0])
         m.update_params(w)
-        got, logits = m.greedy_generate(prompt, 6, collect_logits=True)
-        if rank == 0:
-            want, ref = rai_cpu.greedy_generate(util.build_oracle(cfg, w), torch.from_numpy(prompt.astype(np.int64)), 6, True)
-            err = util.logit_error(logits[0], ref[0]) if dtype == _lib.BF16 else util.rel_error(logits[0], ref[0])
-            same = bool((got.numpy() == want.numpy()).all())
-            print(f"tp{world} {name} dtype {dtype}: prefill logits error {err:.2e}, greedy tokens identical {same}", flush=True)
-            if err > tol or (dtype == _lib.F32 and not same):
-                failures.append(name)
+        # 80 prompt rows go through the peer-memory exchange, 300 rows through NCCL; decode steps
+        # (2 rows) always through the exchange
+        for plen in (40, 150):
+            prompt = synth.prompt(cfg, 2, plen, 31)
+            got, logits = m.greedy_generate(prompt, 6, collect_logits=True)
+            if rank == 0:
+                want, ref = rai_cpu.greedy_generate(util.build_oracle(cfg, w), torch.from_numpy(prompt.astype(np.int64)), 6, True)
+                errs = [util.logit_error(logits[t], ref[t]) if dtype == _lib.BF16 else util.rel_error(logits[t], ref[t])
+                        for t in (0, 1)]
+                same = bool((got.numpy() == want.numpy()).all())
+                print(f"tp{world} {name} dtype {dtype} prompt {plen}: logits error prefill {errs[0]:.2e} first decode "
+                      f"{errs[1]:.2e}, greedy tokens identical {same}", flush=True)
+                if max(errs) > tol or (dtype == _lib.F32 and not same):
+                    failures.append(name)
         m.close()
         dist.barrier()
     dist.destroy_process_group()
