@@ -53,6 +53,16 @@ TINY: Dict[str, dict] = {
     "tiny-qwen2-g7": dict(arch="qwen2", vocab_size=640, hidden_size=896, intermediate_size=768, num_hidden_layers=2,
                      num_attention_heads=7, num_key_value_heads=1, max_position_embeddings=512, sliding_window=4096,
                      rope_theta=1e6, rms_norm_eps=1e-6, hidden_act="silu", tie_word_embeddings=False),
+    # narrow shapes: K = 40 and 64 (less than one 64-wide K slice), N = 40, a 64-row vocabulary
+    "tiny-qwen2-narrow": dict(arch="qwen2", vocab_size=64, hidden_size=128, intermediate_size=40, num_hidden_layers=2,
+                              num_attention_heads=2, num_key_value_heads=2, max_position_embeddings=256,
+                              sliding_window=4096, rope_theta=1e6, rms_norm_eps=1e-6, hidden_act="silu",
+                              tie_word_embeddings=False),
+    # the head layout of the 7B benchmark configuration (28 query heads over 4 KV heads) at small width
+    "tiny-qwen2-28h": dict(arch="qwen2", vocab_size=1024, hidden_size=1792, intermediate_size=1024, num_hidden_layers=2,
+                           num_attention_heads=28, num_key_value_heads=4, max_position_embeddings=256,
+                           sliding_window=4096, rope_theta=1e6, rms_norm_eps=1e-6, hidden_act="silu",
+                           tie_word_embeddings=False),
     "tiny-phi2": dict(arch="phi2", vocab_size=320, hidden_size=160, intermediate_size=640, num_hidden_layers=2,
                  num_attention_heads=2, num_key_value_heads=2, max_position_embeddings=256, rope_theta=1e4,
                  layer_norm_eps=1e-5, hidden_act="gelu_new", partial_rotary_factor=0.4, qk_layernorm=False,

@@ -137,6 +137,16 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// 16 bytes of a peer's exchange buffer, read at system scope so that no stale L1 line can serve it
+__device__ __forceinline__ void load8_sys(const __nv_bfloat16* p, float* v) {
+  uint4 u;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "l"(p) : "memory");
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void load8_sys(const float* p, float* v) { load8(p, v); }  // exchange buffers are bf16 only
+
 template <typename T, int kChunks, bool TP>
 __global__ void norm_vec_kernel(int kind, const T* __restrict__ x, const T* __restrict__ add,
                                 const float* __restrict__ acc, int n_acc, size_t acc_stride,
@@ -179,6 +189,7 @@ __global__ void norm_vec_kernel(int kind, const T* __restrict__ x, const T* __re
     }
     __syncthreads();
     if (tp_seq_s == 0xffffffffu) return;  // a peer never arrived: leave the outputs alone, the host sees the status
+    __threadfence_system();  // every thread's reads of the peers' buffers stay behind the flag reads
     tp_off = (size_t)(tp_seq_s & 1u) * tp.slot_elems;
   }
   float v[kChunks][8];
@@ -206,7 +217,7 @@ __global__ void norm_vec_kernel(int kind, const T* __restrict__ x, const T* __re
     if (TP) {  // the peers' partial sums, read over NVLink, added in rank order on every rank alike
       float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       for (int r = 0; r < tp.size; ++r) {
-        load8(reinterpret_cast<const T*>(tp.xbuf[r]) + tp_off + base + ch * 8, t);
+        load8_sys(reinterpret_cast<const T*>(tp.xbuf[r]) + tp_off + base + ch * 8, t);
 #pragma unroll
         for (int i = 0; i < 8; ++i) sum[i] += t[i];
       }

@@ -30,7 +30,8 @@ def tol(dtype, ref):
 
 
 # (m, n, k): decode-sized (swapped operands), the tile edges, prefill-sized (normal operands), ragged
-SHAPES = [(1, 256, 128), (8, 384, 320), (64, 1152, 896), (64, 128, 64), (16, 136, 72), (100, 520, 256),
+SHAPES = [(2, 192, 256), (2, 256, 64), (2, 256, 40), (2, 64, 256), (80, 256, 40), (2, 40, 256),  # 8-way shard shapes
+          (1, 256, 128), (8, 384, 320), (64, 1152, 896), (64, 128, 64), (16, 136, 72), (100, 520, 256),
           (128, 512, 512), (200, 264, 192), (257, 512, 256), (300, 1000, 328), (1024, 768, 512), (640, 2048, 1024)]
 
 
@@ -52,7 +53,7 @@ def test_linear_matches_oracle(cuda, dtype, m, n, k):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("act", [_lib.ACT_SILU, _lib.ACT_GELU_TANH])
-@pytest.mark.parametrize("m,n,k", [(1, 256, 128), (16, 200, 192), (64, 640, 896), (128, 384, 256), (130, 384, 256),
+@pytest.mark.parametrize("m,n,k", [(2, 40, 256), (2, 80, 256), (80, 40, 256), (1, 256, 128), (16, 200, 192), (64, 640, 896), (128, 384, 256), (130, 384, 256),
                                    (512, 1024, 512), (300, 328, 136)])
 def test_gated_linear_matches_oracle(cuda, dtype, act, m, n, k):
     x, w, w2, _, _ = make(m, n, k, dtype, m + n + act)
@@ -101,3 +102,23 @@ def test_linear_rejects_bad_k(cuda):
     out = torch.empty(4, 16, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(_lib.RaiB200Error):
         _lib.call("rb_linear", cuda.ctx, P(x), P(w), None, None, P(out), 4, 16, 12, _lib.ACT_NONE, _lib.BF16)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_decode_sized_linear_over_many_seeds(cuda, seed):
+    """The same tiny decode GEMMs on fresh data every time: a result that depends on what the previous
+    launch left in shared or tensor memory would show up here."""
+    for m, n, k in ((2, 192, 256), (2, 256, 64), (2, 256, 40), (2, 64, 256)):
+        x, w, _, b, _ = make(m, n, k, torch.bfloat16, 1000 * seed + n + k)
+        out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+        _lib.call("rb_linear", cuda.ctx, P(x), P(w), P(b), None, P(out), m, n, k, _lib.ACT_NONE, _lib.BF16)
+        cuda.synchronize()
+        ref = rai_cpu.linear(x.cpu().float(), w.cpu().float(), b.cpu().float())
+        assert float((out.cpu().float() - ref).abs().max()) <= tol(torch.bfloat16, ref), (m, n, k)
+    x, w, w2, _, _ = make(2, 40, 256, torch.bfloat16, seed)
+    out = torch.empty(2, 40, dtype=torch.bfloat16, device="cuda")
+    _lib.call("rb_gated_linear", cuda.ctx, P(x), P(w), P(w2), P(out), 2, 40, 256, _lib.ACT_SILU, _lib.BF16)
+    cuda.synchronize()
+    xf = x.cpu().float()
+    ref = rai_cpu.silu(xf @ w.cpu().float().t()) * (xf @ w2.cpu().float().t())
+    assert float((out.cpu().float() - ref).abs().max()) <= tol(torch.bfloat16, ref)

@@ -62,6 +62,9 @@ CASES = [  # (nq, nkv, d, rot, batch, prompt, decode steps)
     (8, 1, 256, 256, 2, 65, 2),    # gemma: MQA, head_dim 256
     (4, 4, 128, 128, 1, 1, 4),     # one-token prompt
     (14, 2, 64, 64, 2, 640, 2),    # long enough for several KV splits at decode
+    (1, 1, 64, 64, 2, 40, 6),      # one query head on one KV head (an 8-way shard of a small model)
+    (1, 1, 64, 64, 2, 64, 6),
+    (1, 1, 64, 64, 2, 100, 6),
 ]
 
 
