@@ -18,6 +18,7 @@
 #include <algorithm>
 
 #include "ctx.h"
+#include "ptx.cuh"
 
 namespace rb {
 
@@ -56,17 +57,21 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int D, bool DECODE>
+// TMA = true: K/V tiles arrive by tiled bulk copies (one elected thread, completion on an mbarrier)
+// in the 128-byte-swizzled layout [D/64 column blocks][64 keys][128 bytes]; the copy engine keeps
+// far more bytes in flight than 16-byte cp.async requests through the load/store unit can.
+// TMA = false: padded rows filled with cp.async (head sizes that are not a multiple of 64).
+template <int D, bool DECODE, bool TMA = false>
 struct ACfg {
   static constexpr int kDP = D + 8;                      // padded row: conflict-free ldmatrix
-  static constexpr int kRowBytes = kDP * 2;
+  static constexpr int kRowBytes = kDP * 2;              // Q rows always, K/V rows when !TMA
   static constexpr int kStages = (DECODE && D <= 128) ? 3 : 2;
   static constexpr int kQRows = DECODE ? 16 : 64;
-  static constexpr int kTileBytes = kTile * kRowBytes;   // one of K or V
+  static constexpr int kTileBytes = TMA ? kTile * D * 2 : kTile * kRowBytes;   // one of K or V
   static constexpr int kStageBytes = 2 * kTileBytes;
   static constexpr int kQBytes = kQRows * kRowBytes;
   static constexpr int kMergeBytes = DECODE ? (4 * 16 * D + 2 * 4 * 16) * 4 : 0;
-  static constexpr int kPipeBytes = kStages * kStageBytes + kQBytes;
+  static constexpr int kPipeBytes = kStages * kStageBytes + kQBytes + (TMA ? 1024 : 0);
   static constexpr int kSmemBytes = kPipeBytes > kMergeBytes ? kPipeBytes : kMergeBytes;
   static constexpr bool kQInRegs = D <= 128;
   static constexpr int kKeysPerWarp = DECODE ? 16 : 64;
@@ -85,17 +90,31 @@ struct AParams {
   bf16* out;
   float* part_o;   // [batch*q_heads][n_splits][D]
   float* part_ml;  // [batch*q_heads][n_splits][2]
+  uint32_t* status;
 };
 
-template <int D, bool DECODE>
-__global__ void __launch_bounds__(128, (D <= 128) ? 2 : 1) attention_kernel(const AParams p) {
-  using C = ACfg<D, DECODE>;
+template <int D, bool DECODE, bool TMA>
+__global__ void __launch_bounds__(128, (D <= 128) ? 2 : 1)
+attention_kernel(const AParams p, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
+  using C = ACfg<D, DECODE, TMA>;
   extern __shared__ __align__(16) uint8_t smem[];
-  uint8_t* q_s = smem;
-  uint8_t* kv_s = smem + C::kQBytes;
+  __shared__ __align__(8) uint64_t full_bar[C::kStages];
+  __shared__ volatile uint32_t abort_flag;
+  // K/V stages first (1024-byte aligned for the swizzled layout), Q after them
+  uint8_t* kv_s = TMA ? reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~uintptr_t(1023)) : smem;
+  uint8_t* q_s = kv_s + C::kStages * C::kStageBytes;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   pdl_launch_dependents();
+  if (TMA && threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) ptx::mbar_init(&full_bar[s], 1);
+    abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+    ptx::tma_prefetch_desc(&tm_k);
+    ptx::tma_prefetch_desc(&tm_v);
+  }
+  if (TMA) __syncthreads();
   pdl_wait();  // q and the newest K/V rows come from the kernel before this one
 
   int b, head, kvh, q0 = 0, split = 0;
@@ -136,7 +155,26 @@ __global__ void __launch_bounds__(128, (D <= 128) ? 2 : 1) attention_kernel(cons
       else *reinterpret_cast<uint4*>(q_s + r * C::kRowBytes + c * 16) = make_uint4(0, 0, 0, 0);
     }
   }
+  int armed_it[C::kStages];  // thread 0: iteration whose tile was last requested into each stage
+#pragma unroll
+  for (int s = 0; s < C::kStages; ++s) armed_it[s] = -1;
   auto load_tile = [&](int tile, int stage) {
+    if (TMA) {
+      if (threadIdx.x == 0) {
+        armed_it[stage] = tile - tile_lo;
+        const int page = p.block_table[(size_t)b * p.pages_per_seq + tile];
+        const int y = (page * p.kv_heads + kvh) * kTile;  // first row of this (page, KV head) in the layer
+        uint8_t* ks = kv_s + stage * C::kStageBytes;
+        uint8_t* vs = ks + C::kTileBytes;
+        ptx::mbar_expect_tx(&full_bar[stage], C::kStageBytes);
+#pragma unroll
+        for (int cb = 0; cb < D / 64; ++cb) {
+          ptx::tma_load_2d(ks + cb * (kTile * 128), &tm_k, &full_bar[stage], cb * 64, y);
+          ptx::tma_load_2d(vs + cb * (kTile * 128), &tm_v, &full_bar[stage], cb * 64, y);
+        }
+      }
+      return;
+    }
     const int page = p.block_table[(size_t)b * p.pages_per_seq + tile];
     const size_t off = ((size_t)page * p.kv_heads + kvh) * kTile * D;
     const bf16* ksrc = p.k + off;
@@ -149,6 +187,11 @@ __global__ void __launch_bounds__(128, (D <= 128) ? 2 : 1) attention_kernel(cons
       cp_async16(s_u32(ks + r * C::kRowBytes + c * 16), ksrc + (size_t)r * D + c * 8);
       cp_async16(s_u32(vs + r * C::kRowBytes + c * 16), vsrc + (size_t)r * D + c * 8);
     }
+  };
+  // byte offset of the 16-byte chunk holding (key, dcol..dcol+8) inside a K or V tile
+  auto tile_off = [&](int key, int dc) -> int {
+    if (TMA) return (dc >> 6) * (kTile * 128) + key * 128 + ((((dc & 63) >> 3) ^ (key & 7)) << 4);
+    return key * C::kRowBytes + dc * 2;
   };
   // prologue: Q + the first kStages-1 tiles, one commit group each
 #pragma unroll
@@ -170,6 +213,7 @@ __global__ void __launch_bounds__(128, (D <= 128) ? 2 : 1) attention_kernel(cons
   else { lim[0] = base + q0 + qrow0 + g; lim[1] = lim[0] + 8; }
 
   bool q_loaded = false;
+  bool aborted = false;
   for (int tile = tile_lo; tile < tile_hi; ++tile) {
     const int it = tile - tile_lo;
     {  // keep kStages-1 tiles in flight
@@ -177,8 +221,14 @@ __global__ void __launch_bounds__(128, (D <= 128) ? 2 : 1) attention_kernel(cons
       if (nxt < tile_hi) load_tile(nxt, (it + C::kStages - 1) % C::kStages);
       cp_async_commit();
     }
-    cp_async_wait<C::kStages - 1>();
-    __syncthreads();
+    if (TMA) {
+      if (it == 0) cp_async_wait<0>();  // Q
+      const bool mine = ptx::mbar_wait(&full_bar[it % C::kStages], (uint32_t)(it / C::kStages) & 1u, &abort_flag);
+      if (!__syncthreads_and(mine)) { aborted = true; break; }  // uniform decision: nobody computes on a tile that never came
+    } else {
+      cp_async_wait<C::kStages - 1>();
+      __syncthreads();
+    }
     if (C::kQInRegs && !q_loaded) {
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk)
@@ -205,7 +255,7 @@ __global__ void __launch_bounds__(128, (D <= 128) ? 2 : 1) attention_kernel(cons
           uint32_t bb[4];
           const int key = kw0 + np * 16 + (lane & 7) + ((lane >> 4) << 3);
           const int dc = kk * 16 + (((lane >> 3) & 1) << 3);
-          ldsm_x4(bb, s_u32(ks + key * C::kRowBytes + dc * 2));
+          ldsm_x4(bb, s_u32(ks + tile_off(key, dc)));
           mma16816(s[2 * np], a, bb[0], bb[1]);
           mma16816(s[2 * np + 1], a, bb[2], bb[3]);
         }
@@ -253,7 +303,7 @@ __global__ void __launch_bounds__(128, (D <= 128) ? 2 : 1) attention_kernel(cons
           uint32_t bb[4];
           const int key = kw0 + k2 * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
           const int dc = dp * 16 + ((lane >> 4) << 3);
-          ldsm_x4_t(bb, s_u32(vs + key * C::kRowBytes + dc * 2));
+          ldsm_x4_t(bb, s_u32(vs + tile_off(key, dc)));
           mma16816(o[2 * dp], pa[k2], bb[0], bb[1]);
           mma16816(o[2 * dp + 1], pa[k2], bb[2], bb[3]);
         }
@@ -261,6 +311,19 @@ __global__ void __launch_bounds__(128, (D <= 128) ? 2 : 1) attention_kernel(cons
     __syncthreads();  // the stage is overwritten by the next iteration's prefetch
   }
   cp_async_wait<0>();
+  if (TMA && aborted) {
+    // a tile never arrived: report, give copies already handed to the copy engine a bounded chance to land
+    // (the stages are about to be reused as merge space or released), and produce no output
+    if (threadIdx.x == 0) {
+      p.status[0] = (uint32_t)(-RB_ERR_TIMEOUT); p.status[1] = 0xA77Eu; p.status[2] = blockIdx.x; p.status[3] = blockIdx.z;
+      volatile uint32_t never = 0;
+#pragma unroll
+      for (int s = 0; s < C::kStages; ++s)
+        if (armed_it[s] >= 0) ptx::mbar_wait(&full_bar[s], (uint32_t)(armed_it[s] / C::kStages) & 1u, &never);
+    }
+    __syncthreads();
+    return;
+  }
 
   // row sums across the quad
 #pragma unroll
@@ -341,6 +404,27 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
   }
 }
 
+// Launches attention_kernel<D, DECODE> with tiled-copy loading when the head size allows it.
+template <int D, bool DECODE>
+int launch_attn_kernel(rb_ctx* ctx, rb_kv_cache* c, const AParams& p, dim3 grid) {
+  constexpr bool kTma = (D % 64) == 0;
+  using C = ACfg<D, DECODE, kTma>;
+  auto kern = attention_kernel<D, DECODE, kTma>;
+  static bool set = false;
+  if (!set) { RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes)); set = true; }
+  CUtensorMap none{};
+  const CUtensorMap *tk = &none, *tv = &none;
+  if (kTma) {
+    // one map per layer and operand: rows are (page, KV head, token), 64-row x 64-column boxes
+    const int64_t rows = (int64_t)c->num_pages * c->kv_heads * kTile;
+    RB_TRY(tmap_2d_bf16(ctx, p.k, rows, D, D, kTile, &tk));
+    RB_TRY(tmap_2d_bf16(ctx, p.v, rows, D, D, kTile, &tv));
+  }
+  RB_CUDA(launch_kernel(kern, grid, dim3(128), (size_t)C::kSmemBytes, ctx->stream, ctx->pdl, p, *tk, *tv));
+  ctx->launches++;
+  return RB_OK;
+}
+
 struct Scratch {
   float* ptr = nullptr;
   size_t bytes = 0;
@@ -351,22 +435,12 @@ std::map<int, Scratch>& scratch_by_device() {
 }
 
 template <int D>
-int launch_attention(rb_ctx* ctx, AParams& p, int batch, int max_len) {
+int launch_attention(rb_ctx* ctx, rb_kv_cache* c, AParams& p, int batch, int max_len) {
   if (p.s_new > 1) {
-    using C = ACfg<D, false>;
-    auto kern = attention_kernel<D, false>;
-    static bool set = false;
-    if (!set) { RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes)); set = true; }
     dim3 grid((unsigned)((p.s_new + 63) / 64), (unsigned)p.q_heads, (unsigned)batch);
     p.n_splits = 1;
-    RB_CUDA(launch_kernel(kern, grid, dim3(128), (size_t)C::kSmemBytes, ctx->stream, ctx->pdl, p));
-    ctx->launches++;
-    return RB_OK;
+    return launch_attn_kernel<D, false>(ctx, c, p, grid);
   }
-  using C = ACfg<D, true>;
-  auto kern = attention_kernel<D, true>;
-  static bool set = false;
-  if (!set) { RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes)); set = true; }
   // Split the keys of a sequence over several blocks only when (sequence, KV head) pairs alone leave
   // the GPU under-filled: one long block per pair keeps its copy pipeline full and needs no merge.
   const int splits = attention_decode_splits(ctx, batch, p.kv_heads, max_len);
@@ -384,8 +458,7 @@ int launch_attention(rb_ctx* ctx, AParams& p, int batch, int max_len) {
     p.part_ml = sc.ptr + (size_t)batch * p.q_heads * splits * D;
   }
   dim3 grid((unsigned)splits, (unsigned)p.kv_heads, (unsigned)batch);
-  RB_CUDA(launch_kernel(kern, grid, dim3(128), (size_t)C::kSmemBytes, ctx->stream, ctx->pdl, p));
-  ctx->launches++;
+  RB_TRY((launch_attn_kernel<D, true>(ctx, c, p, grid)));
   if (splits > 1) {
     RB_CUDA(launch_kernel(attention_merge_kernel, dim3((unsigned)(batch * p.q_heads)), dim3(128), 0, ctx->stream, ctx->pdl,
                           (const float*)p.part_o, (const float*)p.part_ml, splits, D, p.out));
@@ -412,10 +485,7 @@ static __device__ __align__(256) float g_static_attn_scratch[kStaticScratchFloat
 static float* g_static_attn_scratch_dev[64] = {};
 
 template <int D>
-static int launch_attention_decode_static(rb_ctx* ctx, AParams& p, int batch, int max_len, float* scratch) {
-  using C = ACfg<D, true>;
-  auto kern = attention_kernel<D, true>;
-  RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+static int launch_attention_decode_static(rb_ctx* ctx, rb_kv_cache* c, AParams& p, int batch, int max_len, float* scratch) {
   const int tiles = std::max(1, (max_len + kTile - 1) / kTile);
   const int work = batch * p.kv_heads;
   const int slots = 2 * ctx->sm_count;
@@ -436,8 +506,7 @@ static int launch_attention_decode_static(rb_ctx* ctx, AParams& p, int batch, in
     p.part_ml = scratch + (size_t)batch * p.q_heads * splits * D;
   }
   dim3 grid((unsigned)splits, (unsigned)p.kv_heads, (unsigned)batch);
-  RB_CUDA(launch_kernel(kern, grid, dim3(128), (size_t)C::kSmemBytes, ctx->stream, ctx->pdl, p));
-  ctx->launches++;
+  RB_TRY((launch_attn_kernel<D, true>(ctx, c, p, grid)));
   if (splits > 1) {
     RB_CUDA(launch_kernel(attention_merge_kernel, dim3((unsigned)(batch * p.q_heads)), dim3(128), 0, ctx->stream, ctx->pdl,
                           (const float*)p.part_o, (const float*)p.part_ml, splits, D, p.out));
@@ -476,16 +545,17 @@ int attention_mma_bf16(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, in
   p.group = q_heads / c->kv_heads;
   p.scale_log2 = scale * kLog2e;
   p.out = (bf16*)out;
+  p.status = ctx->status_dev;
   RB_REQUIRE(p.group >= 1 && p.group <= 16 && q_heads % c->kv_heads == 0,
              "attention: %d query heads per KV head unsupported (1..16)", p.group);
   int max_len = 0;
   for (int b = 0; b < batch; ++b) max_len = std::max(max_len, c->host_lens[b]);
   switch (c->head_dim) {
-    case 64: return launch_attention<64>(ctx, p, batch, max_len);
-    case 80: return launch_attention<80>(ctx, p, batch, max_len);
-    case 96: return launch_attention<96>(ctx, p, batch, max_len);
-    case 128: return launch_attention<128>(ctx, p, batch, max_len);
-    case 256: return launch_attention<256>(ctx, p, batch, max_len);
+    case 64: return launch_attention<64>(ctx, c, p, batch, max_len);
+    case 80: return launch_attention<80>(ctx, c, p, batch, max_len);
+    case 96: return launch_attention<96>(ctx, c, p, batch, max_len);
+    case 128: return launch_attention<128>(ctx, c, p, batch, max_len);
+    case 256: return launch_attention<256>(ctx, c, p, batch, max_len);
   }
   return fail(RB_ERR_UNIMPLEMENTED, "attention: head_dim %d has no tensor-core kernel (64, 80, 96, 128, 256)",
               c->head_dim);
@@ -532,12 +602,13 @@ extern "C" int32_t rb_attention_decode_static(rb_ctx* ctx, const void* q, rb_kv_
   p.group = q_heads / c->kv_heads;
   p.scale_log2 = scale * kLog2e;
   p.out = (bf16*)out;
+  p.status = ctx->status_dev;
   switch (c->head_dim) {
-    case 64: return launch_attention_decode_static<64>(ctx, p, batch, max_len, scratch);
-    case 80: return launch_attention_decode_static<80>(ctx, p, batch, max_len, scratch);
-    case 96: return launch_attention_decode_static<96>(ctx, p, batch, max_len, scratch);
-    case 128: return launch_attention_decode_static<128>(ctx, p, batch, max_len, scratch);
-    case 256: return launch_attention_decode_static<256>(ctx, p, batch, max_len, scratch);
+    case 64: return launch_attention_decode_static<64>(ctx, c, p, batch, max_len, scratch);
+    case 80: return launch_attention_decode_static<80>(ctx, c, p, batch, max_len, scratch);
+    case 96: return launch_attention_decode_static<96>(ctx, c, p, batch, max_len, scratch);
+    case 128: return launch_attention_decode_static<128>(ctx, c, p, batch, max_len, scratch);
+    case 256: return launch_attention_decode_static<256>(ctx, c, p, batch, max_len, scratch);
   }
   return fail(RB_ERR_UNIMPLEMENTED, "rb_attention_decode_static: head_dim %d has no kernel (64, 80, 96, 128, 256)", c->head_dim);
 }
