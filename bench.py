@@ -334,6 +334,7 @@ def run_ours(args):
         sampler.stop()
     clocks = sampler.summary(t_begin, t_end) if rank == 0 else None
     decode_tok_s = B * K / (decode_ms / 1e3)
+    graph_active = bool(_lib.lib().rb_model_decode_graph_active(model._m))
 
     # ---- per-kernel-class timing of the same steps (event pair around every launch; separate pass)
     classes = ["gemm", "attention", "norm", "rope_kv", "embed", "argmax", "other"]
@@ -454,6 +455,7 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(args, cfg, world), "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
         "roofline": roofline, "cpu_baseline": cpu, "prefill": prefill,
+        "decode_step_is_cuda_graph": graph_active,
         "tokens_checksum": int(out_tokens.to(torch.int64).sum().item()),
     }
     print(json.dumps(line), flush=True)

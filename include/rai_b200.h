@@ -285,6 +285,9 @@ int32_t rb_model_generate_step(rb_model* m, const uint32_t* tokens_host, int32_t
  * [batch] at position pos; writes out_dev [steps, batch].  Asynchronous. */
 int32_t rb_model_decode_loop(rb_model* m, const uint32_t* tokens_dev, int32_t batch, int32_t pos, int32_t steps,
                              uint32_t* out_dev);
+/* 1 when single-token steps (rb_model_decode_loop, rb_model_generate_step with seq == 1) currently replay
+ * a captured CUDA graph, 0 when they are issued launch by launch.  No counterpart in the reference. */
+int32_t rb_model_decode_graph_active(rb_model* m);
 int32_t rb_model_clear_kv_cache(rb_model* m);
 rb_kv_cache* rb_model_kv_cache(rb_model* m);
 /* Number of kernels the library launched on this context since creation (self-reported count). */

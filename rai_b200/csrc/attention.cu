@@ -486,14 +486,7 @@ static float* g_static_attn_scratch_dev[64] = {};
 
 template <int D>
 static int launch_attention_decode_static(rb_ctx* ctx, rb_kv_cache* c, AParams& p, int batch, int max_len, float* scratch) {
-  const int tiles = std::max(1, (max_len + kTile - 1) / kTile);
-  const int work = batch * p.kv_heads;
-  const int slots = 2 * ctx->sm_count;
-  int splits = 1;
-  if (work * 4 < slots * 3) {
-    splits = (slots + work - 1) / work;
-    splits = std::max(1, std::min(splits, std::min(tiles / 2, 32)));
-  }
+  const int splits = attention_decode_splits(ctx, batch, p.kv_heads, max_len);
   p.n_splits = splits;
   if (splits > 1) {
     const size_t need = (size_t)batch * p.q_heads * splits * (D + 2);
@@ -516,17 +509,23 @@ static int launch_attention_decode_static(rb_ctx* ctx, rb_kv_cache* c, AParams& 
 }
 
 int attention_decode_splits(rb_ctx* ctx, int batch, int kv_heads, int max_len) {
+  // One block per (sequence, KV head) keeps its copy pipeline full and needs no merge; splitting the
+  // keys only pays when those pairs under-fill the GPU.  Cost model in units of key tiles: a launch
+  // runs ceil(blocks / resident blocks) waves, each as long as one block's tiles plus a fixed start-up,
+  // and a split launch pays for the merge kernel.
   const int tiles = std::max(1, (max_len + kTile - 1) / kTile);
   const int work = batch * kv_heads;
   const int slots = 2 * ctx->sm_count;
-  int splits = 1;
-  if (work * 4 < slots * 3) {
-    splits = (slots + work - 1) / work;
-    splits = std::max(1, std::min(splits, std::min(tiles / 2, 32)));  // at least 2 tiles per split
+  int best = 1;
+  double best_cost = 1e30;
+  for (int s = 1; s <= std::min(tiles, 32); ++s) {
+    const int waves = (work * s + slots - 1) / slots;
+    const double cost = (double)waves * ((tiles + s - 1) / s + 2.0) + (s > 1 ? 1.5 : 0.0);
+    if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
   }
   static const int forced = getenv("RAI_B200_ATTN_SPLITS") ? atoi(getenv("RAI_B200_ATTN_SPLITS")) : 0;
-  if (forced > 0) splits = std::max(1, std::min(forced, tiles));
-  return splits;
+  if (forced > 0) best = std::max(1, std::min(forced, tiles));
+  return best;
 }
 
 int attention_mma_bf16(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, int batch, int s_new, int q_heads,

@@ -108,6 +108,9 @@ int tp_publish(rb_ctx* ctx, const TpPeers& tp, const float* acc, int n_acc, cons
                int64_t hidden);
 int norm_tp(rb_ctx* ctx, const TpPeers& tp, int kind, const void* x, const void* w, const void* b, float eps, int64_t rows,
             int64_t hidden, void* out, void* sum_out);
+// decoder_kernels.cu: out[r, j] = act(sum_s part[s][r][j] + bias[j]) (* sum_s part[s][r][j + n_out] when gated)
+int act_from_partials(rb_ctx* ctx, const float* part, int n_split, int64_t rows, int64_t n_all, int64_t n_out, bool gated,
+                      const void* bias, int act, void* out);
 int attention_decode_splits(rb_ctx* ctx, int batch, int kv_heads, int max_len);
 int attention_simple(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, int batch, int s_new, int q_heads,
                      float scale, void* out, int dtype);

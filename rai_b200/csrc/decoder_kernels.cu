@@ -310,6 +310,43 @@ __global__ void tp_publish_kernel(const float* __restrict__ acc, int n_acc, size
     *reinterpret_cast<volatile uint32_t*>(tp.flags[threadIdx.x] + (seq & 1u) * kTpMaxRanks + tp.rank) = seq;
 }
 
+
+// Finishes an MLP up-projection that was computed as split-K partials over [gate; up]: sums the slabs in
+// a fixed order, adds the bias, applies the activation (hlops/activations.rs:20-32) and the gating
+// product (qwen2.rs:101-103).  8 outputs per thread.
+__global__ void act_from_partials_kernel(const float* __restrict__ part, int n_split, size_t slab, int n_all, int n_out,
+                                         int gated, const __nv_bfloat16* __restrict__ bias, int act,
+                                         __nv_bfloat16* __restrict__ out, int64_t total_chunks) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int chunks_per_row = n_out >> 3;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total_chunks; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / chunks_per_row;
+    const int j = (int)(i % chunks_per_row) * 8;
+    float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, u[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, t[8];
+    for (int s = 0; s < n_split; ++s) {
+      load8(part + (size_t)s * slab + (size_t)r * n_all + j, t);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) g[k] += t[k];
+      if (gated) {
+        load8(part + (size_t)s * slab + (size_t)r * n_all + n_out + j, t);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) u[k] += t[k];
+      }
+    }
+    if (bias) { load8(bias + j, t);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) g[k] += t[k]; }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      // gate and up are tensors of the model dtype before the product in the reference; round like the fused kernel does not
+      const float a = act_apply(act, g[k]);
+      g[k] = gated ? a * u[k] : a;
+    }
+    store8(out + (size_t)r * n_out + j, g);
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // Head split + RoPE + paged KV append.  One block per token.  Pairing is (i, i + rot/2) within the
 // first `rot` lanes of each head ("rotate_half", qwen2.rs:33-38); lanes >= rot pass through
@@ -623,6 +660,19 @@ int norm_tp(rb_ctx* ctx, const TpPeers& tp, int kind, const void* x, const void*
   RB_REQUIRE(rows > 0 && rows <= kTpMaxRows, "norm_tp: %lld rows exceed the exchange buffer", (long long)rows);
   ProfScope prof(ctx, RB_PROF_NORM, (double)rows * hidden * 2.0 * (3 + tp.size), 0.0);
   RB_TRY(norm_launch<__nv_bfloat16>(ctx, kind, x, nullptr, nullptr, 0, nullptr, w, b, eps, rows, hidden, out, sum_out, &tp));
+  ctx->launches++;
+  return RB_OK;
+}
+
+int act_from_partials(rb_ctx* ctx, const float* part, int n_split, int64_t rows, int64_t n_all, int64_t n_out, bool gated,
+                      const void* bias, int act, void* out) {
+  RB_REQUIRE(part && out && rows > 0 && n_out > 0 && (n_out % 8) == 0 && (n_all % 4) == 0, "act_from_partials: bad shape");
+  ProfScope prof(ctx, RB_PROF_OTHER, (double)rows * (4.0 * n_split * n_all + 2.0 * n_out), 0.0);
+  const int64_t chunks = rows * (n_out / 8);
+  const int blocks = (int)std::min<int64_t>((chunks + 127) / 128, 8 * ctx->sm_count);
+  RB_CUDA(launch_kernel(act_from_partials_kernel, dim3((unsigned)blocks), dim3(128), 0, ctx->stream, ctx->pdl, part, n_split,
+                        (size_t)rows * n_all, (int)n_all, (int)n_out, gated ? 1 : 0, (const __nv_bfloat16*)bias, act,
+                        (__nv_bfloat16*)out, chunks));
   ctx->launches++;
   return RB_OK;
 }

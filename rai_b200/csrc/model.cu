@@ -266,6 +266,29 @@ int linear_into_residual(rb_model* m, Pending& pend, const void* x, const void* 
 
 int forward_body(rb_model* m, const uint32_t* tokens, int batch, int seq, void* logits_out);
 
+// act = activation(x . W1^T [+ b1]) [* (x . Wup^T)]  -- the first half of MLP::fwd.  When the fused kernel
+// would leave most SMs idle (decode-sized rows and few 128-row weight tiles, i.e. small or sharded
+// intermediate sizes) the product is computed as split-K partials over [gate; up] and a small kernel
+// applies bias, activation and gating.
+int mlp_up(rb_model* m, const LayerW& w, int64_t rows) {
+  const rb_model_config& c = m->cfg;
+  rb_ctx* ctx = m->ctx;
+  const bool gated = c.arch != RB_ARCH_PHI2;
+  const int H = c.hidden_size;
+  const int64_t n_all = gated ? 2 * (int64_t)m->inter_l : m->inter_l;
+  const int64_t fused_items = (m->inter_l + 127) / 128;
+  int s = 1;
+  if (c.dtype == RB_BF16 && !ctx->debug_simple && rows <= 256 && fused_items * 4 < (int64_t)ctx->sm_count * 3) {
+    s = rb_linear_pick_splits(ctx, rows, n_all, H);
+    if ((size_t)s * rows * n_all <= m->scratch_floats) {
+      RB_TRY(rb_linear_partials(ctx, m->xn, w.gate, m->scratch, rows, n_all, H, s));
+      return act_from_partials(ctx, m->scratch, s, rows, n_all, m->inter_l, gated, w.fc1_b, c.hidden_act, m->act);
+    }
+  }
+  if (gated) return rb_gated_linear(ctx, m->xn, w.gate, w.up, m->act, rows, m->inter_l, H, c.hidden_act, c.dtype);
+  return rb_linear(ctx, m->xn, w.gate, w.fc1_b, nullptr, m->act, rows, m->inter_l, H, c.hidden_act, c.dtype);
+}
+
 int forward_impl(rb_model* m, const uint32_t* tokens, int batch, int seq, int pos, void* logits_out) {
   const rb_model_config& c = m->cfg;
   rb_ctx* ctx = m->ctx;
@@ -318,10 +341,10 @@ int forward_body(rb_model* m, const uint32_t* tokens, int batch, int seq, void* 
     RB_TRY(linear_into_residual(m, pend, m->attn, w.o, w.o_b, rows, H, (int64_t)m->nq_l * d));
     if (c.arch == RB_ARCH_PHI2) {
       // parallel block (phi2.rs:293-299): the MLP reads the same normed input as the attention
-      RB_TRY(rb_linear(ctx, m->xn, w.gate, w.fc1_b, nullptr, m->act, rows, m->inter_l, H, c.hidden_act, c.dtype));
+      RB_TRY(mlp_up(m, w, rows));
     } else {
       RB_TRY(norm_point(m, pend, w.ln2_w, nullptr, rows, m->xn));  // post_attention_layernorm
-      RB_TRY(rb_gated_linear(ctx, m->xn, w.gate, w.up, m->act, rows, m->inter_l, H, c.hidden_act, c.dtype));
+      RB_TRY(mlp_up(m, w, rows));
     }
     RB_TRY(linear_into_residual(m, pend, m->act, w.down, w.down_b, rows, H, m->inter_l));
   }
@@ -498,8 +521,13 @@ extern "C" int32_t rb_model_create(rb_ctx* ctx, const rb_model_config* cfg, rb_m
     if (qkv_bias) A(m->nqkv_l, &w.qkv_b);
     A((int64_t)H * m->nq_l * d, &w.o);
     if (phi2) A(H, &w.o_b);
-    A((int64_t)Il * H, &w.gate);
-    if (!phi2) A((int64_t)Il * H, &w.up); else A(Il, &w.fc1_b);
+    if (!phi2) {  // gate and up in one buffer, gate rows first: one skinny GEMM can then cover both
+      A((int64_t)2 * Il * H, &w.gate);
+      w.up = st == RB_OK ? (void*)((char*)w.gate + (size_t)Il * H * m->es) : nullptr;
+    } else {
+      A((int64_t)Il * H, &w.gate);
+      A(Il, &w.fc1_b);
+    }
     A((int64_t)H * Il, &w.down);
     if (phi2) A(H, &w.down_b);
     A(H, &w.ln1_w);
@@ -761,6 +789,9 @@ int decode_step(rb_model* m, int batch) {
     }
     if (st != RB_OK || ce != cudaSuccess || !m->step_graph) {
       // capture is an optimisation: fall back to plain launches for the rest of this model's life
+      if (getenv("RAI_B200_VERBOSE"))
+        fprintf(stderr, "rai_b200: decode-step capture failed (status %d: %s; cuda: %s); using plain launches\n", st,
+                st != RB_OK ? rb_last_error() : "-", cudaGetErrorString(ce));
       cudaGetLastError();
       m->step_graph = nullptr;
       m->use_graph = false;
@@ -802,6 +833,8 @@ int on_own_stream(rb_model* m, F fn) {
 }
 
 }  // namespace
+
+extern "C" int32_t rb_model_decode_graph_active(rb_model* m) { return (m && m->step_graph) ? 1 : 0; }
 
 extern "C" int32_t rb_model_generate_step(rb_model* m, const uint32_t* tokens_host, int32_t batch, int32_t seq,
                                           int32_t pos, uint32_t* next_host) {

@@ -59,8 +59,8 @@ def test_static_scratch_attention_matches_rb_attention_twice(cuda, nq, nkv, d, b
 
 
 def test_static_scratch_attention_refuses_shapes_beyond_its_array(cuda):
-    # 2 sequences x 64 heads x 32 splits x (256 + 2) floats = 1,056,768 > 1 Mi floats
-    nq, nkv, d, batch, ctx_len = 64, 4, 256, 2, 4200
+    # 4 sequences x 64 heads x 17 splits x (256 + 2) floats = 1,122,816 > 1 Mi floats
+    nq, nkv, d, batch, ctx_len = 64, 4, 256, 4, 4200
     cache = make_cache(cuda, 1, nkv, d, batch, ctx_len + 8)
     _lib.call("rb_kv_cache_set_len", cache, batch, ctx_len)
     q = torch.zeros(batch, nq * d, dtype=torch.bfloat16, device="cuda")
