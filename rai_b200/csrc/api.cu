@@ -68,6 +68,10 @@ extern "C" int32_t rb_init(int32_t device, rb_ctx** out) {
   RB_CUDA(cudaMemset(c->argmax_count, 0, kArgmaxRows * sizeof(unsigned int)));
   const char* dbg = getenv("RAI_B200_SIMPLE");
   c->debug_simple = dbg && dbg[0] == '1';
+  const char* dg = getenv("RAI_B200_SIMPLE_GEMM");
+  const char* da = getenv("RAI_B200_SIMPLE_ATTN");
+  c->debug_simple_gemm = c->debug_simple || (dg && dg[0] == '1');
+  c->debug_simple_attn = c->debug_simple || (da && da[0] == '1');
   const char* pdl = getenv("RAI_B200_PDL");
   c->pdl = !(pdl && pdl[0] == '0');
   *out = c;
@@ -268,7 +272,7 @@ extern "C" int32_t rb_linear(rb_ctx* ctx, const void* x, const void* w, const vo
   const double es = (double)dtype_size(dtype);
   ProfScope prof(ctx, RB_PROF_GEMM, es * ((double)n * k + (double)m * k + (double)m * n * (residual ? 2 : 1) + (bias ? n : 0)),
                  2.0 * m * n * k);
-  if (dtype == RB_BF16 && !ctx->debug_simple) return gemm_tc_bf16(ctx, a);
+  if (dtype == RB_BF16 && !ctx->debug_simple_gemm) return gemm_tc_bf16(ctx, a);
   return gemm_simple(ctx, a, dtype);
 }
 
@@ -281,7 +285,7 @@ extern "C" int32_t rb_gated_linear(rb_ctx* ctx, const void* x, const void* wg, c
   a.m = m; a.n = n; a.k = k; a.act = act;
   const double es = (double)dtype_size(dtype);
   ProfScope prof(ctx, RB_PROF_GEMM, es * (2.0 * n * k + (double)m * k + (double)m * n), 4.0 * m * n * k);
-  if (dtype == RB_BF16 && !ctx->debug_simple) return gemm_tc_bf16(ctx, a);
+  if (dtype == RB_BF16 && !ctx->debug_simple_gemm) return gemm_tc_bf16(ctx, a);
   return gemm_simple(ctx, a, dtype);
 }
 
@@ -294,7 +298,7 @@ extern "C" int32_t rb_linear_partials(rb_ctx* ctx, const void* x, const void* w,
   a.m = m; a.n = n; a.k = k;
   a.n_split = n_split; a.partials = true;
   ProfScope prof(ctx, RB_PROF_GEMM, 2.0 * ((double)n * k + (double)m * k) + 4.0 * n_split * m * n, 2.0 * m * n * k);
-  if (!ctx->debug_simple) return gemm_tc_bf16(ctx, a);
+  if (!ctx->debug_simple_gemm) return gemm_tc_bf16(ctx, a);
   return gemm_simple(ctx, a, RB_BF16);
 }
 
@@ -323,6 +327,6 @@ extern "C" int32_t rb_attention(rb_ctx* ctx, const void* q, rb_kv_cache* c, int3
   const double es = (double)dtype_size(dtype), d = c->head_dim;
   ProfScope prof(ctx, RB_PROF_ATTENTION,
                  es * (2.0 * kv_tokens * c->kv_heads * d + 2.0 * batch * s_new * q_heads * d), 4.0 * pairs * q_heads * d);
-  if (dtype == RB_BF16 && !ctx->debug_simple) return attention_mma_bf16(ctx, q, c, layer, batch, s_new, q_heads, scale, out);
+  if (dtype == RB_BF16 && !ctx->debug_simple_attn) return attention_mma_bf16(ctx, q, c, layer, batch, s_new, q_heads, scale, out);
   return attention_simple(ctx, q, c, layer, batch, s_new, q_heads, scale, out, dtype);
 }

@@ -22,7 +22,8 @@ struct rb_ctx {
   // argmax across blocks: running best (key << 32 | index) and arrival count per row; self-resetting
   unsigned long long* argmax_best = nullptr;
   unsigned int* argmax_count = nullptr;
-  bool debug_simple = false;  // RAI_B200_SIMPLE=1: route bf16 through the plain kernels (debugging aid)
+  bool debug_simple = false;
+  bool debug_simple_gemm = false, debug_simple_attn = false;  // RAI_B200_SIMPLE_GEMM / _ATTN: one kernel family only  // RAI_B200_SIMPLE=1: route bf16 through the plain kernels (debugging aid)
   // Optional per-launch timing (rb_profile_start / rb_profile_read): an event pair around each launch.
   struct ProfRec { int cls; cudaEvent_t a, b; double bytes, flops; };
   bool profiling = false;
