@@ -46,6 +46,9 @@ def parse_args():
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--profile-steps", type=int, default=8)
+    ap.add_argument("--shard-of", type=int, default=0,
+                    help="developer aid: time ONE rank's shard of an N-way tensor-parallel model on one GPU, without its "
+                         "peers (results are not the model's outputs; the line is labelled)")
     ap.add_argument("--skip-fill", action="store_true",
                     help="leave the KV cache zero-filled instead of prefilling it (same traffic; for profiler runs)")
     return ap.parse_args()
@@ -267,7 +270,10 @@ def run_ours(args):
     cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], max_seq)
     max_tokens = max(B * chunk, 0 if args.skip_prefill else PB * PS)
     dev = Cuda(local)
-    model = Model(cfg, _lib.BF16, dev, max(B, PB), max_seq, max_tokens, tp_rank=rank, tp_size=world)
+    if args.shard_of > 1 and world == 1:
+        os.environ["RAI_B200_SHARD_ONLY"] = "1"
+    model = Model(cfg, _lib.BF16, dev, max(B, PB), max_seq, max_tokens, tp_rank=rank,
+                  tp_size=args.shard_of if (args.shard_of > 1 and world == 1) else world)
     if world > 1:
         uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
         if rank == 0:
@@ -456,6 +462,7 @@ def run_ours(args):
         "config": workload_config(args, cfg, world), "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
         "roofline": roofline, "cpu_baseline": cpu, "prefill": prefill,
         "decode_step_is_cuda_graph": graph_active,
+        "shard_only_of": args.shard_of or None,
         "tokens_checksum": int(out_tokens.to(torch.int64).sum().item()),
     }
     print(json.dumps(line), flush=True)

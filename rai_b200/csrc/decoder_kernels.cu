@@ -189,7 +189,7 @@ __global__ void norm_vec_kernel(int kind, const T* __restrict__ x, const T* __re
     }
     __syncthreads();
     if (tp_seq_s == 0xffffffffu) return;  // a peer never arrived: leave the outputs alone, the host sees the status
-    __threadfence_system();  // every thread's reads of the peers' buffers stay behind the flag reads
+    // thread 0's acquire loads plus the barrier order every thread's (system-scope) reads below behind the flags
     tp_off = (size_t)(tp_seq_s & 1u) * tp.slot_elems;
   }
   float v[kChunks][8];

@@ -162,6 +162,7 @@ struct rb_model {
   void* xchg_base = nullptr;
   void* peer_base[kTpMaxRanks] = {};
   bool use_exchange = false;
+  bool shard_only = false;  // RAI_B200_SHARD_ONLY=1: run one rank's shard without its peers (timing of per-rank kernels)
   // One decode step (advance lengths, forward of the tokens in `ids`, argmax back into `ids`)
   // captured as a CUDA graph and replayed; re-captured when the batch or the launch plan changes.
   cudaGraphExec_t step_graph = nullptr;
@@ -198,6 +199,7 @@ int norm_kind(const rb_model* m) {
 }
 
 int allreduce(rb_model* m, void* buf, size_t count) {
+  if (m->shard_only) return RB_OK;  // one rank of a group run alone (profiling aid): the sum is just its own term
   RB_NCCL(nccl().AllReduce(buf, buf, count, m->cfg.dtype == RB_BF16 ? kNcclBfloat16 : kNcclFloat32, kNcclSum, m->comm,
                            m->ctx->stream));
   return RB_OK;
@@ -366,6 +368,7 @@ int forward_body(rb_model* m, const uint32_t* tokens, int batch, int seq, void* 
   } else {
     RB_TRY(rb_linear(ctx, m->xn, head_w, m->lm_head_b, nullptr, m->logits_g, batch, m->vocab_l, H, RB_ACT_NONE, c.dtype));
     void* gathered = (char*)m->logits_g + (size_t)batch * m->vocab_l * m->es;
+    if (!m->shard_only)
     RB_NCCL(nccl().AllGather(m->logits_g, gathered, (size_t)batch * m->vocab_l * m->es, kNcclUint8, m->comm, ctx->stream));
     const int64_t n = (int64_t)c.tp_size * batch * m->vocab_l;
     const int blocks = (int)std::min<int64_t>((n + 255) / 256, 4096);
@@ -396,6 +399,7 @@ extern "C" int32_t rb_tp_unique_id(void* out128) {
 extern "C" int32_t rb_model_tp_init(rb_model* m, const void* id, int32_t id_bytes) {
   RB_REQUIRE(m && id && id_bytes == 128, "rb_model_tp_init: expects a 128-byte ncclUniqueId");
   if (m->cfg.tp_size <= 1) return RB_OK;
+  if (m->shard_only) return RB_OK;
   RB_TRY(nccl_load());
   UniqueId u;
   memcpy(u.bytes, id, 128);
@@ -636,6 +640,24 @@ extern "C" int32_t rb_model_create(rb_ctx* ctx, const rb_model_config* cfg, rb_m
     W(m->scratch_floats * sizeof(float), (void**)&m->scratch);
   }
   if (st != RB_OK) { rb_model_destroy(m); return st; }
+  {
+    const char* so = getenv("RAI_B200_SHARD_ONLY");
+    m->shard_only = tp > 1 && so && so[0] == '1';
+    if (m->shard_only && c.dtype == RB_BF16 && (H % 8) == 0) {
+      // the exchange kernels still run, against a group of one (this rank's own region)
+      const size_t slot_elems = (size_t)kTpMaxRows * H;
+      st = dev_alloc(m, 512 + 2 * slot_elems * 2, &m->xchg_base, true);
+      if (st != RB_OK) { rb_model_destroy(m); return st; }
+      TpPeers& p = m->peers;
+      p.flags[0] = (uint32_t*)m->xchg_base;
+      p.seq = (uint32_t*)m->xchg_base + 64;
+      p.block_count = p.seq + 32;
+      p.xbuf[0] = (const char*)m->xchg_base + 512;
+      p.rank = 0; p.size = 1; p.slot_elems = (int64_t)slot_elems;
+      m->peer_base[0] = m->xchg_base;
+      m->use_exchange = true;
+    }
+  }
   RB_CUDA(cudaStreamSynchronize(ctx->stream));
   *out = m;
   return RB_OK;
