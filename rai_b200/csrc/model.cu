@@ -342,7 +342,9 @@ int forward_body(rb_model* m, const uint32_t* tokens, int batch, int seq, void* 
     RB_TRY(rb_attention(ctx, m->q, m->cache, l, batch, seq, m->nq_l, scale, m->attn, c.dtype));
     RB_TRY(linear_into_residual(m, pend, m->attn, w.o, w.o_b, rows, H, (int64_t)m->nq_l * d));
     if (c.arch == RB_ARCH_PHI2) {
-      // parallel block (phi2.rs:293-299): the MLP reads the same normed input as the attention
+      // parallel block (phi2.rs:293-299): the MLP reads the same normed input as the attention.
+      // The attention output may still sit in the split-K scratch that the MLP is about to reuse: fold it first.
+      if (pend.acc) RB_TRY(norm_point(m, pend, nullptr, nullptr, rows, nullptr));
       RB_TRY(mlp_up(m, w, rows));
     } else {
       RB_TRY(norm_point(m, pend, w.ln2_w, nullptr, rows, m->xn));  // post_attention_layernorm
