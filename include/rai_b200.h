@@ -188,6 +188,16 @@ int32_t rb_attention_decode_static(rb_ctx* ctx, const void* q_dev, rb_kv_cache* 
  * total order, the LAST index among equal maxima.  Bit-exact by construction. */
 int32_t rb_argmax_rows(rb_ctx* ctx, const void* logits_dev, int32_t dtype, int64_t rows, int64_t cols,
                        uint32_t* out_dev);
+/* The sampling the examples' loops actually run (examples/qwen2/src/main.rs:42-53,84-93): when
+ * penalty >= 1, every token id present in the row's context window (a set: a repeated id counts once) has
+ * its float32 logit divided by the penalty when >= 0, multiplied by it otherwise; then sample_argmax.
+ * context_dev is [rows, context_stride] (stride <= 256), of which the first
+ * min(context_count_dev[row], context_stride) slots are valid, in any order.  With eos_token >= 0 and
+ * finished_dev != NULL ([rows] bytes, zero to start), a row that has produced eos_token is marked and
+ * produces it from then on (the example leaves its loop there).  The logits are not modified.  Bit-exact. */
+int32_t rb_sample_greedy(rb_ctx* ctx, const void* logits_dev, int32_t dtype, int64_t rows, int64_t cols, float penalty,
+                         const int32_t* context_dev, int32_t context_stride, const int32_t* context_count_dev,
+                         int32_t eos_token, uint8_t* finished_dev, uint32_t* out_dev);
 
 /* ======================================================================================
  * Primitive set — the Eval rules of rai-core/src/backend/candle.rs:197-1004 that the decoders'
@@ -285,6 +295,17 @@ int32_t rb_model_generate_step(rb_model* m, const uint32_t* tokens_host, int32_t
  * [batch] at position pos; writes out_dev [steps, batch].  Asynchronous. */
 int32_t rb_model_decode_loop(rb_model* m, const uint32_t* tokens_dev, int32_t batch, int32_t pos, int32_t steps,
                              uint32_t* out_dev);
+/* Sampling used by rb_model_generate_step and rb_model_decode_loop, as in the examples' loops
+ * (examples/qwen2/src/main.rs:74-76,84-96: repeat_penalty 1.10 over repeat_last_n 64, stop at the
+ * end-of-text token).  The library keeps, per sequence, the last repeat_last_n (<= 256) tokens fed to
+ * those two entry points (prompt and generated alike) and applies rb_sample_greedy's rule; a penalty < 1
+ * or repeat_last_n == 0 means plain argmax, eos_token < 0 means no stop rule.  A sequence that produced
+ * eos_token keeps producing it (the batch stays rectangular); rb_model_finished reports which have.
+ * The history restarts when a call passes pos == 0 and on rb_model_clear_kv_cache.  Default: plain argmax,
+ * which is what "greedy" means in the benchmark configurations. */
+int32_t rb_model_set_sampling(rb_model* m, float repeat_penalty, int32_t repeat_last_n, int32_t eos_token);
+/* flags_host[b] = 1 when sequence b has produced the end-of-sequence token.  Synchronous. */
+int32_t rb_model_finished(rb_model* m, int32_t batch, uint8_t* flags_host);
 /* 1 when single-token steps (rb_model_decode_loop, rb_model_generate_step with seq == 1) currently replay
  * a captured CUDA graph, 0 when they are issued launch by launch.  No counterpart in the reference. */
 int32_t rb_model_decode_graph_active(rb_model* m);

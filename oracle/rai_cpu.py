@@ -462,20 +462,63 @@ def build(cfg: Config, params: Dict[str, torch.Tensor]):
 # generation loop of the examples (examples/qwen2/src/main.rs:32-53,74-99)
 # --------------------------------------------------------------------------------------
 
+def total_order_keys(values) -> "np.ndarray":
+    """f32::total_cmp as an unsigned key: flip all bits of negatives, set the sign bit of the rest, so
+    that -NaN < -inf < ... < -0.0 < +0.0 < ... < +inf < +NaN compares as plain integers."""
+    import numpy as np
+    u = np.ascontiguousarray(np.asarray(values, dtype=np.float32)).view(np.uint32)
+    return np.where(u & np.uint32(0x80000000), ~u, u | np.uint32(0x80000000))
+
+
 def sample_argmax(logits: torch.Tensor) -> int:
-    """examples/qwen2/src/main.rs:32-40 — `max_by(total_cmp)` returns the LAST index among equal
-    maxima (NaN handling of total_cmp is not restated: the inputs here are finite)."""
-    v = logits.reshape(-1)
-    m = v.max()
-    return int(torch.nonzero(v == m).max())
+    """examples/qwen2/src/main.rs:32-40 — `max_by(total_cmp)`: the maximum under the IEEE total order,
+    and the LAST index among equal maxima (Iterator::max_by returns the last of equal elements)."""
+    import numpy as np
+    k = total_order_keys(logits.reshape(-1).float().numpy())
+    return int(np.nonzero(k == k.max())[0].max())
 
 
 def apply_repeat_penalty(logits: torch.Tensor, penalty: float, context) -> torch.Tensor:
-    """examples/qwen2/src/main.rs:42-53."""
-    out = logits.clone()
+    """examples/qwen2/src/main.rs:42-53: every token id present in `context` (a set, so once each) has
+    its float32 logit divided by the float32 penalty when >= 0 and multiplied by it otherwise."""
+    import numpy as np
+    out = logits.float().clone().numpy()
+    p = np.float32(penalty)
     for t in set(int(c) for c in context):
-        out[t] = out[t] / penalty if out[t] >= 0 else out[t] * penalty
-    return out
+        out[t] = np.float32(out[t]) / p if out[t] >= 0 else np.float32(out[t]) * p
+    return torch.from_numpy(out)
+
+
+def generate_with_penalty(model, prompt: torch.Tensor, steps: int, penalty: float, last_n: int, eos: int = -1,
+                          collect_logits: bool = False):
+    """The generation loop of examples/qwen2/src/main.rs:74-99 for each row of a batch: logits to float32,
+    repeat penalty over the last `last_n` tokens of (prompt + generated) when penalty >= 1, argmax, stop at
+    `eos`.  A finished row keeps emitting `eos` so that the batch stays rectangular (the example handles one
+    sequence and leaves the loop).  Returns [B, steps] tokens (and the raw per-step logits when asked)."""
+    model.clear_kv_cache()
+    b, s = prompt.shape
+    tokens = [[int(t) for t in prompt[i]] for i in range(b)]
+    finished = [False] * b
+    out, all_logits = [], []
+    ids, pos = prompt, 0
+    for _ in range(steps):
+        logits = model.forward(ids, pos).reshape(b, -1).float()
+        pos += ids.shape[1]
+        nxt = []
+        for i in range(b):
+            row = logits[i]
+            if penalty >= 1.0:
+                row = apply_repeat_penalty(row, penalty, tokens[i][max(0, len(tokens[i]) - last_n):])
+            t = eos if finished[i] else sample_argmax(row)
+            finished[i] = finished[i] or t == eos
+            tokens[i].append(t)
+            nxt.append(t)
+        out.append(torch.tensor(nxt, dtype=torch.int64))
+        if collect_logits:
+            all_logits.append(logits.clone())
+        ids = out[-1].reshape(b, 1)
+    res = torch.stack(out, dim=1)
+    return (res, torch.stack(all_logits)) if collect_logits else res
 
 
 def greedy_generate(model, prompt: torch.Tensor, steps: int, collect_logits: bool = False):

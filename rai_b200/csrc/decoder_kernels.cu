@@ -504,18 +504,71 @@ __device__ __forceinline__ uint32_t total_order_key(float f) {
 // Each row is split over gridDim.x blocks; a block folds its segment into a 64-bit (key << 32 | index)
 // candidate, merges it into the row's running best with atomicMax (order-independent, so the result
 // is deterministic), and the last block to arrive writes the index and resets the scratch words.
-template <typename T>
+//
+// PEN = true adds the examples' repeat penalty (examples/qwen2/src/main.rs:42-53,84-88): the token ids in
+// the row's context window form a set (a hash set in shared memory, so a repeated id is penalised once);
+// a member's float32 logit is divided by the penalty when >= 0 and multiplied by it otherwise before it
+// competes.  The penalised value never goes back to the logits' storage type, exactly like the host code,
+// which penalises a float32 copy.  `eos`/`finished` give the loop's stop rule per row: a row that has
+// produced `eos` keeps producing it.
+struct SampleArgs {
+  const int32_t* context = nullptr;        // [rows, context_stride] token ids
+  const int32_t* context_count = nullptr;  // [rows] ids pushed so far; min(count, stride) slots are valid
+  int context_stride = 0;
+  float penalty = 0.f;
+  int32_t eos = -1;
+  uint8_t* finished = nullptr;             // [rows] or null
+};
+constexpr int kSampleTableSlots = 1024;    // hash slots, 4x the largest context window
+constexpr int kSampleMaxContext = 256;
+
+__device__ __forceinline__ uint32_t sample_emit(const SampleArgs& sa, int r, uint32_t idx) {
+  if (sa.eos >= 0 && sa.finished) {
+    if (sa.finished[r]) idx = (uint32_t)sa.eos;
+    else if (idx == (uint32_t)sa.eos) sa.finished[r] = 1;
+  }
+  return idx;
+}
+
+template <typename T, bool PEN>
 __global__ void argmax_rows_kernel(const T* __restrict__ x, int64_t cols, uint32_t* __restrict__ out,
-                                   unsigned long long* __restrict__ best_g, unsigned int* __restrict__ count_g) {
+                                   unsigned long long* __restrict__ best_g, unsigned int* __restrict__ count_g,
+                                   SampleArgs sa) {
   __shared__ unsigned long long best[32];
+  __shared__ int32_t table[PEN ? kSampleTableSlots : 1];
   pdl_launch_dependents();
   pdl_wait();
   const int r = blockIdx.y;
   const T* row = x + (size_t)r * cols;
   const int64_t seg = ((cols + gridDim.x - 1) / gridDim.x + 7) & ~int64_t(7);
   const int64_t c0 = (int64_t)blockIdx.x * seg, c1 = min(cols, c0 + seg);
+  if (PEN) {
+    for (int i = threadIdx.x; i < kSampleTableSlots; i += blockDim.x) table[i] = -1;
+    __syncthreads();
+    const int valid = min(sa.context_count[r], sa.context_stride);
+    for (int i = threadIdx.x; i < valid; i += blockDim.x) {
+      const int32_t tok = sa.context[(size_t)r * sa.context_stride + i];
+      if (tok < 0) continue;
+      uint32_t h = ((uint32_t)tok * 0x9E3779B1u) >> 22;
+      for (int probe = 0; probe < kSampleTableSlots; ++probe) {   // at most 256 of 1024 slots ever fill
+        const int32_t prev = atomicCAS(&table[h], -1, tok);
+        if (prev == -1 || prev == tok) break;
+        h = (h + 1) & (kSampleTableSlots - 1);
+      }
+    }
+    __syncthreads();
+  }
   unsigned long long loc = 0;
   auto consider = [&](float f, int64_t i) {
+    if (PEN) {
+      uint32_t h = ((uint32_t)i * 0x9E3779B1u) >> 22;
+      for (int probe = 0; probe < kSampleTableSlots; ++probe) {
+        const int32_t t = table[h];
+        if (t == -1) break;
+        if (t == (int32_t)i) { f = (f >= 0.f) ? __fdiv_rn(f, sa.penalty) : __fmul_rn(f, sa.penalty); break; }
+        h = (h + 1) & (kSampleTableSlots - 1);
+      }
+    }
     const unsigned long long cand = ((unsigned long long)total_order_key(f) << 32) | (uint32_t)i;
     loc = cand > loc ? cand : loc;
   };
@@ -548,7 +601,7 @@ __global__ void argmax_rows_kernel(const T* __restrict__ x, int64_t cols, uint32
       loc = other > loc ? other : loc;
     }
     if (lane == 0) {
-      if (gridDim.x == 1) { out[r] = (uint32_t)(loc & 0xffffffffull); return; }
+      if (gridDim.x == 1) { out[r] = sample_emit(sa, r, (uint32_t)(loc & 0xffffffffull)); return; }
       atomicMax(&best_g[r], loc);
       __threadfence();
       const unsigned int arrived = atomicAdd(&count_g[r], 1u);
@@ -556,7 +609,7 @@ __global__ void argmax_rows_kernel(const T* __restrict__ x, int64_t cols, uint32
         __threadfence();
         const unsigned long long fin = atomicExch(&best_g[r], 0ull);  // read and reset for the next call
         count_g[r] = 0u;
-        out[r] = (uint32_t)(fin & 0xffffffffull);
+        out[r] = sample_emit(sa, r, (uint32_t)(fin & 0xffffffffull));
       }
     }
   }
@@ -773,14 +826,22 @@ extern "C" int32_t rb_rope_kv_append(rb_ctx* ctx, const void* qkv, const float* 
 }
 
 template <typename T>
-static int argmax_launch(rb_ctx* ctx, const void* logits, int64_t rows, int64_t cols, uint32_t* out) {
+static int argmax_launch(rb_ctx* ctx, const void* logits, int64_t rows, int64_t cols, uint32_t* out, SampleArgs sa) {
   // enough blocks per row to fill the GPU, at least ~2K elements each
   int per_row = (int)std::min<int64_t>(std::max<int64_t>(1, (2 * ctx->sm_count + rows - 1) / rows), (cols + 2047) / 2048);
   per_row = std::max(1, std::min(per_row, 64));
+  const bool pen = sa.context != nullptr;
   for (int64_t r0 = 0; r0 < rows; r0 += kArgmaxRows) {
     const int64_t n = std::min<int64_t>(kArgmaxRows, rows - r0);
-    RB_CUDA(launch_kernel(argmax_rows_kernel<T>, dim3((unsigned)per_row, (unsigned)n), dim3(256), 0, ctx->stream, ctx->pdl,
-                          (const T*)logits + r0 * cols, cols, out + r0, ctx->argmax_best, ctx->argmax_count));
+    SampleArgs part = sa;
+    if (pen) { part.context += r0 * sa.context_stride; part.context_count += r0; }
+    if (part.finished) part.finished += r0;
+    if (pen)
+      RB_CUDA(launch_kernel(argmax_rows_kernel<T, true>, dim3((unsigned)per_row, (unsigned)n), dim3(256), 0, ctx->stream,
+                            ctx->pdl, (const T*)logits + r0 * cols, cols, out + r0, ctx->argmax_best, ctx->argmax_count, part));
+    else
+      RB_CUDA(launch_kernel(argmax_rows_kernel<T, false>, dim3((unsigned)per_row, (unsigned)n), dim3(256), 0, ctx->stream,
+                            ctx->pdl, (const T*)logits + r0 * cols, cols, out + r0, ctx->argmax_best, ctx->argmax_count, part));
     ctx->launches++;
   }
   return RB_OK;
@@ -792,7 +853,31 @@ extern "C" int32_t rb_argmax_rows(rb_ctx* ctx, const void* logits, int32_t dtype
   RB_REQUIRE(rows >= 0 && cols > 0 && cols <= 0xffffffffLL, "rb_argmax_rows: bad sizes");
   if (rows == 0) return RB_OK;
   ProfScope prof(ctx, RB_PROF_ARGMAX, (double)rows * cols * dtype_size(dtype), 0.0);
-  if (dtype == RB_BF16) return argmax_launch<__nv_bfloat16>(ctx, logits, rows, cols, out);
-  if (dtype == RB_F32) return argmax_launch<float>(ctx, logits, rows, cols, out);
+  if (dtype == RB_BF16) return argmax_launch<__nv_bfloat16>(ctx, logits, rows, cols, out, SampleArgs{});
+  if (dtype == RB_F32) return argmax_launch<float>(ctx, logits, rows, cols, out, SampleArgs{});
   return fail(RB_ERR_DTYPE, "rb_argmax_rows: dtype %d unsupported", dtype);
+}
+
+extern "C" int32_t rb_sample_greedy(rb_ctx* ctx, const void* logits, int32_t dtype, int64_t rows, int64_t cols,
+                                    float penalty, const int32_t* context, int32_t context_stride,
+                                    const int32_t* context_count, int32_t eos_token, uint8_t* finished, uint32_t* out) {
+  RB_REQUIRE(ctx && logits && out, "rb_sample_greedy: null argument");
+  RB_REQUIRE(rows >= 0 && cols > 0 && cols <= 0xffffffffLL, "rb_sample_greedy: bad sizes");
+  if (rows == 0) return RB_OK;
+  SampleArgs sa;
+  // the examples apply the penalty only when it is >= 1 (examples/qwen2/src/main.rs:85)
+  if (penalty >= 1.0f && context_stride > 0) {
+    RB_REQUIRE(context && context_count, "rb_sample_greedy: a penalty needs the context window and its counts");
+    RB_REQUIRE(context_stride <= kSampleMaxContext, "rb_sample_greedy: context window %d exceeds %d tokens", context_stride,
+               kSampleMaxContext);
+    sa.context = context;
+    sa.context_count = context_count;
+    sa.context_stride = context_stride;
+    sa.penalty = penalty;
+  }
+  if (eos_token >= 0 && finished) { sa.eos = eos_token; sa.finished = finished; }
+  ProfScope prof(ctx, RB_PROF_ARGMAX, (double)rows * cols * dtype_size(dtype), 0.0);
+  if (dtype == RB_BF16) return argmax_launch<__nv_bfloat16>(ctx, logits, rows, cols, out, sa);
+  if (dtype == RB_F32) return argmax_launch<float>(ctx, logits, rows, cols, out, sa);
+  return fail(RB_ERR_DTYPE, "rb_sample_greedy: dtype %d unsupported", dtype);
 }

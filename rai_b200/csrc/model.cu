@@ -111,6 +111,20 @@ __global__ void advance_lens_kernel(int32_t* lens, int n, int delta) {
   if (i < n) lens[i] += delta;
 }
 
+// The `tokens` vector of the examples' loop (examples/qwen2/src/main.rs:66,92), of which only the last `cap`
+// entries per sequence are ever read (`tokens[start_at..]`, main.rs:86-87): a ring per sequence, written at
+// (count + s) % cap.  Membership is all the penalty needs, so the order inside the ring is irrelevant.
+__global__ void history_push_kernel(const uint32_t* __restrict__ ids, int batch, int seq, int32_t* __restrict__ hist,
+                                    int32_t* __restrict__ count, int cap) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= batch) return;
+  const int c = count[b];
+  for (int s = max(0, seq - cap); s < seq; ++s) hist[(size_t)b * cap + (c + s) % cap] = (int32_t)ids[(size_t)b * seq + s];
+  int n = c + seq;
+  if (n >= 2 * cap) n = cap + n % cap;  // same slot arithmetic, still "full", and bounded
+  count[b] = n;
+}
+
 // out[b, r*vl + j] = gathered[r, b, j]  (vocabulary shards back into rows of logits)
 template <typename T>
 __global__ void unshard_logits_kernel(const T* __restrict__ g, T* __restrict__ out, int tp, int batch, int vl) {
@@ -171,6 +185,13 @@ struct rb_model {
   int64_t graph_launches = 0;
   bool use_graph = true;
   cudaEvent_t ev_in = nullptr, ev_out = nullptr;
+  // sampling of the generation entry points (rb_model_set_sampling): repeat penalty over a ring of the
+  // last `rep_last_n` tokens fed per sequence, and the end-of-sequence rule
+  float rep_penalty = 0.f;
+  int rep_last_n = 0;
+  int32_t eos = -1;
+  int32_t *hist = nullptr, *hist_count = nullptr;
+  uint8_t* finished = nullptr;
 };
 
 namespace {
@@ -746,7 +767,42 @@ extern "C" int32_t rb_model_finalize(rb_model* m) {
 
 extern "C" int32_t rb_model_clear_kv_cache(rb_model* m) {
   RB_REQUIRE(m, "rb_model_clear_kv_cache: null model");
+  if (m->hist_count) {
+    RB_CUDA(cudaMemsetAsync(m->hist_count, 0, (size_t)m->cfg.max_batch * sizeof(int32_t), m->ctx->stream));
+    RB_CUDA(cudaMemsetAsync(m->finished, 0, (size_t)m->cfg.max_batch, m->ctx->stream));
+  }
   return rb_kv_cache_reset(m->cache);
+}
+
+extern "C" int32_t rb_model_set_sampling(rb_model* m, float repeat_penalty, int32_t repeat_last_n, int32_t eos_token) {
+  RB_REQUIRE(m, "rb_model_set_sampling: null model");
+  RB_REQUIRE(repeat_last_n >= 0 && repeat_last_n <= 256, "rb_model_set_sampling: repeat_last_n %d outside [0, 256]", repeat_last_n);
+  RB_REQUIRE(eos_token < m->cfg.vocab_size, "rb_model_set_sampling: eos token %d outside the vocabulary", eos_token);
+  RB_REQUIRE(!(repeat_penalty != repeat_penalty), "rb_model_set_sampling: the penalty is NaN");
+  RB_CUDA(cudaStreamSynchronize(m->ctx->stream));
+  // a captured decode step has the old sampler baked in
+  if (m->step_graph) { cudaGraphExecDestroy(m->step_graph); m->step_graph = nullptr; }
+  m->eager_warm_batch = m->eager_warm_plan = 0;
+  if (!m->hist_count) {
+    RB_TRY(dev_alloc(m, (size_t)m->cfg.max_batch * 256 * sizeof(int32_t), (void**)&m->hist, true));
+    RB_TRY(dev_alloc(m, (size_t)m->cfg.max_batch * sizeof(int32_t), (void**)&m->hist_count, true));
+    RB_TRY(dev_alloc(m, (size_t)m->cfg.max_batch, (void**)&m->finished, true));
+  }
+  m->rep_penalty = repeat_penalty;
+  m->rep_last_n = repeat_last_n;
+  m->eos = eos_token < 0 ? -1 : eos_token;
+  RB_CUDA(cudaMemsetAsync(m->hist_count, 0, (size_t)m->cfg.max_batch * sizeof(int32_t), m->ctx->stream));
+  RB_CUDA(cudaMemsetAsync(m->finished, 0, (size_t)m->cfg.max_batch, m->ctx->stream));
+  return RB_OK;
+}
+
+extern "C" int32_t rb_model_finished(rb_model* m, int32_t batch, uint8_t* flags_host) {
+  RB_REQUIRE(m && flags_host, "rb_model_finished: null argument");
+  RB_REQUIRE(batch >= 0 && batch <= m->cfg.max_batch, "rb_model_finished: batch %d exceeds max_batch", batch);
+  if (!m->finished) { memset(flags_host, 0, (size_t)batch); return RB_OK; }
+  RB_CUDA(cudaMemcpyAsync(flags_host, m->finished, (size_t)batch, cudaMemcpyDeviceToHost, m->ctx->stream));
+  RB_CUDA(cudaStreamSynchronize(m->ctx->stream));
+  return RB_OK;
 }
 
 extern "C" int32_t rb_model_forward(rb_model* m, const uint32_t* tokens_dev, int32_t batch, int32_t seq, int32_t pos,
@@ -756,6 +812,32 @@ extern "C" int32_t rb_model_forward(rb_model* m, const uint32_t* tokens_dev, int
 }
 
 namespace {
+
+bool sampling_on(const rb_model* m) { return (m->rep_penalty >= 1.0f && m->rep_last_n > 0) || m->eos >= 0; }
+
+// Forget the tokens seen and the finished marks: a new generation starts (position 0 or a cleared cache).
+int sampling_reset(rb_model* m) {
+  if (!m->hist_count) return RB_OK;
+  RB_CUDA(cudaMemsetAsync(m->hist_count, 0, (size_t)m->cfg.max_batch * sizeof(int32_t), m->ctx->stream));
+  RB_CUDA(cudaMemsetAsync(m->finished, 0, (size_t)m->cfg.max_batch, m->ctx->stream));
+  return RB_OK;
+}
+
+// The tokens about to be fed join the history BEFORE the sampling that follows their forward pass: at
+// that point the examples' `tokens` holds the prompt and every token generated so far (main.rs:84-92).
+int history_push(rb_model* m, const uint32_t* ids, int batch, int seq) {
+  if (!(m->rep_penalty >= 1.0f && m->rep_last_n > 0)) return RB_OK;
+  history_push_kernel<<<(batch + 127) / 128, 128, 0, m->ctx->stream>>>(ids, batch, seq, m->hist, m->hist_count, m->rep_last_n);
+  RB_CUDA(cudaGetLastError());
+  m->ctx->launches++;
+  return RB_OK;
+}
+
+int sample_tokens(rb_model* m, int batch, uint32_t* out) {
+  if (!sampling_on(m)) return rb_argmax_rows(m->ctx, m->logits, m->cfg.dtype, batch, m->cfg.vocab_size, out);
+  return rb_sample_greedy(m->ctx, m->logits, m->cfg.dtype, batch, m->cfg.vocab_size, m->rep_penalty, m->hist, m->rep_last_n,
+                          m->hist_count, m->eos, m->finished, out);
+}
 
 // Whatever host-side state shapes the launches of a decode step: a captured step is reused only
 // while this stays the same (today: how many KV splits the attention uses).
@@ -769,9 +851,10 @@ int decode_step_launches(rb_model* m, int batch) {
   rb_ctx* ctx = m->ctx;
   advance_lens_kernel<<<(batch + 127) / 128, 128, 0, ctx->stream>>>(m->cache->seq_lens, batch, 1);
   ctx->launches++;
+  RB_TRY(history_push(m, m->ids, batch, 1));
   RB_TRY(forward_body(m, m->ids, batch, 1, nullptr));
-  // the greedy token goes straight back into `ids`, the input of the next step
-  return rb_argmax_rows(ctx, m->logits, m->cfg.dtype, batch, m->cfg.vocab_size, m->ids);
+  // the sampled token goes straight back into `ids`, the input of the next step
+  return sample_tokens(m, batch, m->ids);
 }
 
 // One greedy decode step on the tokens in m->ids (result left in m->ids), on the context's current
@@ -873,11 +956,13 @@ extern "C" int32_t rb_model_generate_step(rb_model* m, const uint32_t* tokens_ho
   const int st = on_own_stream(m, [&]() -> int {
     RB_CUDA(cudaMemcpyAsync(m->ids, tokens_host, (size_t)batch * seq * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream));
     const uint32_t* result = m->ids;
+    if (pos == 0) RB_TRY(sampling_reset(m));
     if (single) {
       RB_TRY(decode_step(m, batch));
     } else {
+      RB_TRY(history_push(m, m->ids, batch, seq));
       RB_TRY(forward_impl(m, m->ids, batch, seq, pos, nullptr));
-      RB_TRY(rb_argmax_rows(ctx, m->logits, m->cfg.dtype, batch, m->cfg.vocab_size, m->next_ids));
+      RB_TRY(sample_tokens(m, batch, m->next_ids));
       result = m->next_ids;
     }
     RB_CUDA(cudaMemcpyAsync(next_host, result, (size_t)batch * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
@@ -898,6 +983,7 @@ extern "C" int32_t rb_model_decode_loop(rb_model* m, const uint32_t* tokens_dev,
   rb_ctx* ctx = m->ctx;
   auto body = [&]() -> int {
     RB_CUDA(cudaMemcpyAsync(m->ids, tokens_dev, (size_t)batch * sizeof(uint32_t), cudaMemcpyDeviceToDevice, ctx->stream));
+    if (pos == 0) RB_TRY(sampling_reset(m));
     for (int i = 0; i < steps; ++i) {
       RB_TRY(decode_step(m, batch));
       RB_CUDA(cudaMemcpyAsync(out_dev + (size_t)i * batch, m->ids, (size_t)batch * sizeof(uint32_t),

@@ -145,6 +145,33 @@ class Model:
     def clear_kv_cache(self) -> None:
         _lib.call("rb_model_clear_kv_cache", self._m)
 
+    def set_sampling(self, repeat_penalty: float = 1.10, repeat_last_n: int = 64, eos_token: int = -1) -> None:
+        """The sampling of the examples' loops (examples/qwen2/src/main.rs:74-76,84-96) for generate_step and
+        decode_loop: repeat penalty over the last `repeat_last_n` tokens, then argmax, then the stop rule."""
+        _lib.call("rb_model_set_sampling", self._m, float(repeat_penalty), int(repeat_last_n), int(eos_token))
+
+    def finished(self, batch: int) -> np.ndarray:
+        """Which sequences have produced the end-of-sequence token."""
+        flags = np.zeros((batch,), dtype=np.uint8)
+        _lib.call("rb_model_finished", self._m, int(batch), flags.ctypes.data_as(ctypes.c_void_p))
+        return flags.astype(bool)
+
+    def generate(self, prompt, steps: int) -> np.ndarray:
+        """The examples' generation loop through the library's own entry points: one generate_step for the
+        prompt (host tokens in, sampled token out), then the device-side decode loop.  [B, steps] int64."""
+        ids = np.ascontiguousarray(np.asarray(prompt, dtype=np.int32))
+        b = ids.shape[0]
+        tok_in = torch.from_numpy(ids).pin_memory()
+        first = torch.empty((b,), dtype=torch.int32).pin_memory()
+        self.clear_kv_cache()
+        self.generate_step(tok_in, 0, first)
+        out = [first.numpy().astype(np.int64).reshape(b, 1)]
+        if steps > 1:
+            rest = self.decode_loop(first.to(f"cuda:{self.device.id}"), ids.shape[1], steps - 1)
+            self.device.synchronize()
+            out.append(rest.cpu().numpy().astype(np.int64).T)
+        return np.concatenate(out, axis=1)
+
     def kv_read(self, layer: int, seq: int, kv_head: int, t0: int, n: int):
         """Test hook: K and V of tokens [t0, t0+n) as float32 [n, head_dim] host tensors."""
         d = configs.head_dim(self.cfg)

@@ -112,3 +112,18 @@ def test_mask_matches_reference_loops():
             want = float("-inf") if (i < j or j + win < i) else 0.0
             assert float(m[i, off + j]) == want
     assert torch.all(m[:, :off] == 0)
+
+
+def test_sampling_rules_of_the_examples():
+    """examples/qwen2/src/main.rs:32-53 worked by hand: the penalty divides non-negative logits and multiplies
+    negative ones, once per distinct token id; argmax is the last index of the maximum under total_cmp."""
+    x = torch.tensor([1.0, -1.0, 2.0, 0.0])
+    got = rai_cpu.apply_repeat_penalty(x, 2.0, [0, 1, 1, 3])
+    assert got.tolist() == [0.5, -2.0, 2.0, 0.0]
+    assert rai_cpu.sample_argmax(torch.tensor([1.0, 3.0, 3.0, 2.0])) == 2
+    assert rai_cpu.sample_argmax(torch.tensor([0.0, -0.0, -0.0])) == 0          # +0.0 > -0.0 under the total order
+    assert rai_cpu.sample_argmax(torch.tensor([-0.0, 0.0, 0.0])) == 2
+    assert rai_cpu.sample_argmax(torch.tensor([float("-inf"), float("-inf")])) == 1
+    p = np.float32(1.10)
+    y = rai_cpu.apply_repeat_penalty(torch.tensor([3.3, -3.3]), 1.10, [0, 1])
+    assert y[0].item() == np.float32(np.float32(3.3) / p) and y[1].item() == np.float32(np.float32(-3.3) * p)
