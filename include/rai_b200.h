@@ -69,6 +69,7 @@ enum { RB_RED_SUM = 0, RB_RED_MAX, RB_RED_MIN };
 typedef struct rb_ctx rb_ctx;
 typedef struct rb_kv_cache rb_kv_cache;
 typedef struct rb_model rb_model;
+typedef struct rb_safetensors rb_safetensors;
 
 /* ======================================================================================
  * Context — one per (process, GPU).  Stands in for the device cache of the reference backend
@@ -268,9 +269,30 @@ int32_t rb_model_destroy(rb_model* m);
 /* Tensor::update_by_name, rai-core/src/nn.rs:192-205: copies (and casts to the model dtype) one named
  * parameter; names follow the derive rule of rai-core/src/nn.rs:256-269, e.g.
  * "model.layers.3.self_attn.q_proj.weight".  With tensor parallelism the FULL tensor is passed and
- * the library keeps this rank's shard.  src_dtype is RB_F32 or RB_BF16. */
+ * the library keeps this rank's shard.  src_dtype is RB_F32, RB_BF16, RB_F16 or RB_F64 (the float
+ * types Tensor::from_safetensor accepts, rai-core/src/hlops/from_safetensor.rs:51-91). */
 int32_t rb_model_load_param(rb_model* m, const char* name, const void* data, int32_t on_device, int32_t src_dtype,
                             int32_t rank, const int64_t* shape);
+/* Module::update_by_safetensors, rai-core/src/nn.rs:39-55: every parameter of the model is looked up by
+ * name in the given files (names absent from the model are ignored; a later file wins over an earlier
+ * one, like the reference's map insert) and cast to the model dtype; a parameter found in no file fails
+ * with RB_ERR_PARAM, the reference's Error::ParamNotFound.  The files are mapped, not read: each tensor
+ * goes mapping -> pinned staging -> device in chunks, the host copy of one chunk overlapping the upload
+ * of the previous one, and with tensor parallelism only the rows this rank keeps are uploaded.
+ * Replaces the two whole-tensor host copies of the reference's path (std::fs::read + convert_slice).
+ * Finalises the model on success. */
+int32_t rb_model_load_safetensors(rb_model* m, const char* const* paths, int32_t n_paths);
+
+/* The file reader underneath, usable on its own (host only, no GPU): maps a .safetensors file and
+ * validates its header the way safetensors::SafeTensors::deserialize does (header length, JSON shape,
+ * data_offsets inside the file and equal to numel x element size).  Entries are listed in file order.
+ * rb_safetensors_entry: dtype is an RB_* tag or -1 for a type this library has no tag for; shape8 receives
+ * `rank` extents; data points into the mapping and stays valid until rb_safetensors_close. */
+int32_t rb_safetensors_open(const char* path, rb_safetensors** out);
+int32_t rb_safetensors_close(rb_safetensors* st);
+int32_t rb_safetensors_count(const rb_safetensors* st);
+int32_t rb_safetensors_entry(const rb_safetensors* st, int32_t index, const char** name, int32_t* dtype, int32_t* rank,
+                             int64_t* shape8, const void** data, uint64_t* bytes);
 /* Fails with RB_ERR_PARAM naming the first parameter that was never loaded. */
 int32_t rb_model_finalize(rb_model* m);
 /* Number of parameter names the architecture expects, and the i-th name. */

@@ -53,7 +53,7 @@ _SCALARS = {"int32_t": ctypes.c_int32, "int64_t": ctypes.c_int64, "size_t": ctyp
 def _ctype_of(decl: str):
     decl = decl.strip()
     if "*" in decl:
-        return ctypes.c_char_p if re.match(r"^const\s+char\s*\*", decl) else ctypes.c_void_p
+        return ctypes.c_char_p if decl.count("*") == 1 and re.match(r"^const\s+char\s*\*", decl) else ctypes.c_void_p
     base = decl.split()[0] if not decl.startswith("const") else decl.split()[1]
     return _SCALARS[base]
 

@@ -89,6 +89,14 @@ template <> struct Cvt<__nv_bfloat16> {
   __device__ __forceinline__ static float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
   __device__ __forceinline__ static __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
 };
+template <> struct Cvt<__half> {
+  __device__ __forceinline__ static float to_f(__half v) { return __half2float(v); }
+  __device__ __forceinline__ static __half from_f(float v) { return __float2half_rn(v); }
+};
+template <> struct Cvt<double> {
+  __device__ __forceinline__ static float to_f(double v) { return (float)v; }
+  __device__ __forceinline__ static double from_f(float v) { return (double)v; }
+};
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -391,8 +391,15 @@ int forward_body(rb_model* m, const uint32_t* tokens, int batch, int seq, void* 
   } else {
     RB_TRY(rb_linear(ctx, m->xn, head_w, m->lm_head_b, nullptr, m->logits_g, batch, m->vocab_l, H, RB_ACT_NONE, c.dtype));
     void* gathered = (char*)m->logits_g + (size_t)batch * m->vocab_l * m->es;
-    if (!m->shard_only)
-    RB_NCCL(nccl().AllGather(m->logits_g, gathered, (size_t)batch * m->vocab_l * m->es, kNcclUint8, m->comm, ctx->stream));
+    const size_t shard_bytes = (size_t)batch * m->vocab_l * m->es;
+    if (!m->shard_only) {
+      RB_NCCL(nccl().AllGather(m->logits_g, gathered, shard_bytes, kNcclUint8, m->comm, ctx->stream));
+    } else {
+      // a rank run without its peers: its own vocabulary shard in place, zeros where the others' would be
+      RB_CUDA(cudaMemsetAsync(gathered, 0, shard_bytes * c.tp_size, ctx->stream));
+      RB_CUDA(cudaMemcpyAsync((char*)gathered + shard_bytes * c.tp_rank, m->logits_g, shard_bytes, cudaMemcpyDeviceToDevice,
+                              ctx->stream));
+    }
     const int64_t n = (int64_t)c.tp_size * batch * m->vocab_l;
     const int blocks = (int)std::min<int64_t>((n + 255) / 256, 4096);
     if (c.dtype == RB_BF16)
@@ -727,18 +734,34 @@ static int copy_pieces(rb_model* m, const ParamSpec& sp, const S* src_dev) {
   return RB_OK;
 }
 
+static int copy_pieces_any(rb_model* m, const ParamSpec& sp, const void* src_dev, int32_t src_dtype) {
+  switch (src_dtype) {
+    case RB_F32: return copy_pieces<float>(m, sp, (const float*)src_dev);
+    case RB_BF16: return copy_pieces<__nv_bfloat16>(m, sp, (const __nv_bfloat16*)src_dev);
+    case RB_F16: return copy_pieces<__half>(m, sp, (const __half*)src_dev);
+    case RB_F64: return copy_pieces<double>(m, sp, (const double*)src_dev);
+  }
+  return fail(RB_ERR_DTYPE, "parameter source dtype %d unsupported (F32, BF16, F16, F64)", src_dtype);
+}
+
+static int check_param_shape(const char* name, const ParamSpec& sp, int32_t rank, const int64_t* shape) {
+  const int64_t rows = rank >= 1 ? shape[0] : 1, cols = rank >= 2 ? shape[1] : 1;
+  if (rank != sp.rank || rows != sp.rows || cols != sp.cols)
+    return fail(RB_ERR_SHAPE, "parameter '%s': got shape [%lld, %lld] (rank %d), expected [%lld, %lld] (rank %d)", name,
+                (long long)rows, (long long)cols, rank, (long long)sp.rows, (long long)sp.cols, sp.rank);
+  return RB_OK;
+}
+
 extern "C" int32_t rb_model_load_param(rb_model* m, const char* name, const void* data, int32_t on_device,
                                        int32_t src_dtype, int32_t rank, const int64_t* shape) {
   RB_REQUIRE(m && name && data && shape, "rb_model_load_param: null argument");
   auto it = m->params.find(name);
   if (it == m->params.end()) return fail(RB_ERR_PARAM, "parameter '%s' is not part of this model", name);
   ParamSpec& sp = it->second;
-  RB_REQUIRE(src_dtype == RB_F32 || src_dtype == RB_BF16, "rb_model_load_param: source dtype %d unsupported", src_dtype);
-  const int64_t rows = shape[0], cols = rank >= 2 ? shape[1] : 1;
-  if (rank != sp.rank || rows != sp.rows || cols != sp.cols)
-    return fail(RB_ERR_SHAPE, "parameter '%s': got shape [%lld, %lld] (rank %d), expected [%lld, %lld] (rank %d)", name,
-                (long long)rows, (long long)cols, rank, (long long)sp.rows, (long long)sp.cols, sp.rank);
-  const size_t bytes = (size_t)rows * cols * dtype_size(src_dtype);
+  RB_REQUIRE(src_dtype == RB_F32 || src_dtype == RB_BF16 || src_dtype == RB_F16 || src_dtype == RB_F64,
+             "rb_model_load_param: source dtype %d unsupported", src_dtype);
+  RB_TRY(check_param_shape(name, sp, rank, shape));
+  const size_t bytes = (size_t)sp.rows * sp.cols * dtype_size(src_dtype);
   const void* src = data;
   void* staging = nullptr;
   if (!on_device) {
@@ -747,14 +770,127 @@ extern "C" int32_t rb_model_load_param(rb_model* m, const char* name, const void
     if (st != RB_OK) { rb_free(m->ctx, staging); return st; }
     src = staging;
   }
-  int st = src_dtype == RB_F32 ? copy_pieces<float>(m, sp, (const float*)src)
-                               : copy_pieces<__nv_bfloat16>(m, sp, (const __nv_bfloat16*)src);
+  int st = copy_pieces_any(m, sp, src, src_dtype);
   if (staging) {
     cudaStreamSynchronize(m->ctx->stream);
     cudaFree(staging);
   }
   if (st == RB_OK) sp.loaded = true;
   return st;
+}
+
+namespace {
+
+// Streams host bytes to the device through two pinned buffers: while chunk k is in flight to the GPU the
+// host copies chunk k+1 out of the file mapping (which is where the page faults, i.e. the disk reads, happen).
+struct PinnedPipe {
+  static constexpr size_t kChunk = 32u << 20;
+  void* buf[2] = {nullptr, nullptr};
+  cudaEvent_t done[2] = {nullptr, nullptr};
+  int next = 0;
+  int init() {
+    for (int i = 0; i < 2; ++i) {
+      RB_CUDA(cudaHostAlloc(&buf[i], kChunk, cudaHostAllocDefault));
+      RB_CUDA(cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming));
+    }
+    return RB_OK;
+  }
+  int send(void* dst_dev, const void* src_host, size_t bytes, cudaStream_t stream) {
+    for (size_t off = 0; off < bytes; off += kChunk) {
+      const size_t n = std::min(kChunk, bytes - off);
+      RB_CUDA(cudaEventSynchronize(done[next]));  // the buffer's previous upload has left it
+      memcpy(buf[next], (const char*)src_host + off, n);
+      RB_CUDA(cudaMemcpyAsync((char*)dst_dev + off, buf[next], n, cudaMemcpyHostToDevice, stream));
+      RB_CUDA(cudaEventRecord(done[next], stream));
+      next ^= 1;
+    }
+    return RB_OK;
+  }
+  ~PinnedPipe() {
+    for (int i = 0; i < 2; ++i) {
+      if (done[i]) { cudaEventSynchronize(done[i]); cudaEventDestroy(done[i]); }
+      if (buf[i]) cudaFreeHost(buf[i]);
+    }
+  }
+};
+
+}  // namespace
+
+extern "C" int32_t rb_model_load_safetensors(rb_model* m, const char* const* paths, int32_t n_paths) {
+  RB_REQUIRE(m && paths && n_paths > 0, "rb_model_load_safetensors: null or empty argument");
+  struct Files {
+    std::vector<rb_safetensors*> v;
+    ~Files() { for (rb_safetensors* s : v) rb_safetensors_close(s); }
+  } files;
+  // last file wins for a name that appears in several (the reference inserts into one map, file by file)
+  std::map<std::string, std::pair<int, int>> where;
+  size_t staging_bytes = 0;
+  for (int f = 0; f < n_paths; ++f) {
+    RB_REQUIRE(paths[f], "rb_model_load_safetensors: path %d is null", f);
+    rb_safetensors* st = nullptr;
+    RB_TRY(rb_safetensors_open(paths[f], &st));
+    files.v.push_back(st);
+    for (int i = 0; i < rb_safetensors_count(st); ++i) {
+      const char* name;
+      RB_TRY(rb_safetensors_entry(st, i, &name, nullptr, nullptr, nullptr, nullptr, nullptr));
+      if (m->params.count(name)) where[name] = {f, i};
+    }
+  }
+  for (const std::string& n : m->names)
+    if (!where.count(n) && !m->params[n].loaded)
+      return fail(RB_ERR_PARAM, "parameter '%s' was found in none of the %d safetensors file(s)", n.c_str(), n_paths);
+
+  // rows of the source this rank keeps (all of them without tensor parallelism)
+  struct Job { std::string name; int file, index; int64_t row0, row1; };
+  std::vector<Job> jobs;
+  for (auto& kv : where) {
+    const ParamSpec& sp = m->params[kv.first];
+    int64_t r0 = sp.rows, r1 = 0;
+    for (const Piece& pc : sp.pieces)
+      if (pc.rows > 0 && pc.cols > 0) { r0 = std::min(r0, pc.src_row0); r1 = std::max(r1, pc.src_row0 + pc.rows); }
+    if (r1 <= r0) { r0 = 0; r1 = 0; }
+    jobs.push_back({kv.first, kv.second.first, kv.second.second, r0, r1});
+  }
+  // file order, so that the mapping is read front to back
+  std::sort(jobs.begin(), jobs.end(), [](const Job& a, const Job& b) { return a.file != b.file ? a.file < b.file : a.index < b.index; });
+  for (const Job& j : jobs) {
+    int32_t dtype, rank;
+    int64_t shape[8];
+    const char* name;
+    RB_TRY(rb_safetensors_entry(files.v[j.file], j.index, &name, &dtype, &rank, shape, nullptr, nullptr));
+    const ParamSpec& sp = m->params[j.name];
+    RB_REQUIRE(dtype == RB_F32 || dtype == RB_BF16 || dtype == RB_F16 || dtype == RB_F64,
+               "parameter '%s' is stored as a non-floating type", name);
+    RB_TRY(check_param_shape(name, sp, rank, shape));
+    staging_bytes = std::max(staging_bytes, (size_t)(j.row1 - j.row0) * sp.cols * dtype_size(dtype));
+  }
+
+  rb_ctx* ctx = m->ctx;
+  PinnedPipe pipe;
+  RB_TRY(pipe.init());
+  void* staging = nullptr;
+  if (staging_bytes) RB_TRY(rb_malloc(ctx, staging_bytes, &staging));
+  int st = RB_OK;
+  for (const Job& j : jobs) {
+    int32_t dtype;
+    const void* data;
+    st = rb_safetensors_entry(files.v[j.file], j.index, nullptr, &dtype, nullptr, nullptr, &data, nullptr);
+    if (st != RB_OK) break;
+    ParamSpec& sp = m->params[j.name];
+    const size_t es = dtype_size(dtype), row_bytes = (size_t)sp.cols * es;
+    if (j.row1 > j.row0) {
+      st = pipe.send(staging, (const char*)data + (size_t)j.row0 * row_bytes, (size_t)(j.row1 - j.row0) * row_bytes, ctx->stream);
+      if (st != RB_OK) break;
+      // copy_pieces indexes rows of the whole tensor: hand it the address row 0 would have
+      st = copy_pieces_any(m, sp, (const char*)staging - (size_t)j.row0 * row_bytes, dtype);
+      if (st != RB_OK) break;
+    }
+    sp.loaded = true;
+  }
+  cudaStreamSynchronize(ctx->stream);
+  if (staging) rb_free(ctx, staging);
+  RB_TRY(st);
+  return rb_model_finalize(m);
 }
 
 extern "C" int32_t rb_model_finalize(rb_model* m) {

@@ -71,13 +71,13 @@ class Model:
         self.finalize()
 
     def update_by_safetensors(self, files: Iterable[str]) -> None:
-        """Module::update_by_safetensors (rai-core/src/nn.rs:39-55)."""
-        from safetensors import safe_open
-        for f in files:
-            with safe_open(f, framework="pt") as sf:
-                for k in sf.keys():
-                    self.update_param(k, sf.get_tensor(k))
-        self.finalize()
+        """Module::update_by_safetensors (rai-core/src/nn.rs:39-55) through the library's own reader: the
+        files are mapped and streamed to the GPU, each parameter cast to the model dtype on the device."""
+        paths = [str(f).encode() for f in files]
+        arr = (ctypes.c_char_p * len(paths))(*paths)
+        self.device.use_torch_stream()
+        _lib.call("rb_model_load_safetensors", self._m, arr, len(paths))
+        self._finalized = True
 
     def finalize(self) -> None:
         _lib.call("rb_model_finalize", self._m)
