@@ -46,6 +46,8 @@ def parse_args():
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--profile-steps", type=int, default=8)
+    ap.add_argument("--timeline", default="", help="write a per-kernel device timeline of a few decode steps (as replayed, "
+                    "overlap included) to this JSON file; a tracing pass of its own, never part of the timed region")
     ap.add_argument("--shard-of", type=int, default=0,
                     help="developer aid: time ONE rank's shard of an N-way tensor-parallel model on one GPU, without its "
                          "peers (results are not the model's outputs; the line is labelled)")
@@ -192,6 +194,43 @@ def cpu_decode_sample(cfg, batch, ctx, steps, warmup):
                        f"per-layer {per_layer * 1e3:.0f} ms, outside layers {outside * 1e3:.0f} ms, extrapolated to "
                        f"{full_layers} layers = {step_s:.2f} s/step"),
             "ms_per_step": step_s * 1e3}
+
+
+def decode_timeline(model, dev, rewind, first, T0, path, steps=4):
+    """Kernel start/end times of `steps` decode steps as the device ran them (graph replay, dependent launches
+    overlapping), from the CUDA activity records torch's profiler collects.  Per kernel name: launches, busy time,
+    and the idle gap between the previous kernel's end and this one's start; plus the raw sequence of one step."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    rewind(T0)
+    model.decode_loop(first, T0, 2)
+    dev.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        model.decode_loop(first, T0 + 2, steps)
+        dev.synchronize()
+    evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and e.time_range.end > e.time_range.start]
+    evs.sort(key=lambda e: e.time_range.start)
+    if not evs:
+        json.dump({"error": "no device activity records"}, open(path, "w"))
+        return
+    t0 = evs[0].time_range.start
+    seq, by_name, prev_end = [], {}, None
+    for e in evs:
+        name = e.name.split("(")[0].replace("void ", "").replace("rb::", "").replace("(anonymous namespace)::", "")
+        start, end = e.time_range.start - t0, e.time_range.end - t0
+        gap = None if prev_end is None else start - prev_end
+        prev_end = end if prev_end is None else max(prev_end, end)
+        seq.append({"name": name, "start_us": round(start, 2), "dur_us": round(end - start, 2), "gap_us": None if gap is None else round(gap, 2)})
+        a = by_name.setdefault(name, {"launches": 0, "busy_us": 0.0, "gap_us": 0.0, "overlapped_us": 0.0})
+        a["launches"] += 1
+        a["busy_us"] += end - start
+        if gap is not None:
+            a["gap_us" if gap >= 0 else "overlapped_us"] += abs(gap)
+    span = max(x["start_us"] + x["dur_us"] for x in seq)
+    per_step = {k: {kk: round(vv / steps, 2) for kk, vv in v.items()} for k, v in by_name.items()}
+    n = len(seq) // steps
+    json.dump({"steps": steps, "span_us_per_step": round(span / steps, 1), "per_kernel_per_step": per_step,
+               "one_step": seq[n:2 * n]}, open(path, "w"), indent=1)
 
 
 def run_reference(args):
@@ -357,6 +396,9 @@ def run_ours(args):
                            "gbytes_per_step": out4[2] / PK / 1e9, "avg_launch_us": out4[1] / out4[0] * 1e3,
                            "achieved_gbs": out4[2] / 1e9 / (out4[1] / 1e3) if out4[1] > 0 else None}
     dev.synchronize()
+
+    if args.timeline and rank == 0:
+        decode_timeline(model, dev, rewind, first, T0, args.timeline)
 
     # ---- end to end through the generation-step call: pinned host tokens in, token ids out, per step
     e2e = None

@@ -185,6 +185,17 @@ int32_t rb_attention(rb_ctx* ctx, const void* q_dev, rb_kv_cache* cache, int32_t
 int32_t rb_attention_decode_static(rb_ctx* ctx, const void* q_dev, rb_kv_cache* cache, int32_t layer, int32_t batch,
                                    int32_t q_heads, float scale, void* out_dev);
 
+/* rb_rope_kv_append followed by rb_attention for a single new token per sequence (s_new == 1), the step a
+ * KV-cached decode repeats (qwen2.rs:176-216 with seq_len 1): same inputs, same results bit for bit.  For bf16
+ * caches with head_dim 64, 128 or 256 and a rotary width that is a multiple of 16 both run as ONE kernel: the
+ * attention kernel rotates q and k itself, appends k/v to the cache, and can start fetching old K/V pages
+ * before the projection that feeds it has finished; q_scratch_dev ([batch, q_heads, head_dim]) is then not
+ * touched.  Every other case runs the two calls one after the other, through q_scratch_dev. */
+int32_t rb_rope_attention_decode(rb_ctx* ctx, const void* qkv_dev, const float* acc_dev, int32_t n_acc, const void* bias_dev,
+                                 const float* cos_dev, const float* sin_dev, int32_t rot, int32_t batch, int32_t q_heads,
+                                 rb_kv_cache* cache, int32_t layer, float scale, void* q_scratch_dev, void* out_dev,
+                                 int32_t dtype);
+
 /* sample_argmax, examples/qwen2/src/main.rs:32-40: per row, the index of the maximum under f32
  * total order, the LAST index among equal maxima.  Bit-exact by construction. */
 int32_t rb_argmax_rows(rb_ctx* ctx, const void* logits_dev, int32_t dtype, int64_t rows, int64_t cols,

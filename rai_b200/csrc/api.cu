@@ -72,6 +72,8 @@ extern "C" int32_t rb_init(int32_t device, rb_ctx** out) {
   const char* da = getenv("RAI_B200_SIMPLE_ATTN");
   c->debug_simple_gemm = c->debug_simple || (dg && dg[0] == '1');
   c->debug_simple_attn = c->debug_simple || (da && da[0] == '1');
+  const char* nf = getenv("RAI_B200_FUSE_ROPE");  // RAI_B200_FUSE_ROPE=0: separate RoPE/append and attention launches
+  c->debug_no_fuse = nf && nf[0] == '0';
   const char* pdl = getenv("RAI_B200_PDL");
   c->pdl = !(pdl && pdl[0] == '0');
   *out = c;
@@ -305,6 +307,37 @@ extern "C" int32_t rb_linear_partials(rb_ctx* ctx, const void* x, const void* w,
 extern "C" int32_t rb_linear_pick_splits(rb_ctx* ctx, int64_t m, int64_t n, int64_t k) {
   if (!ctx || m <= 0 || n <= 0 || k <= 0) return 1;
   return gemm_tc_pick_splits(ctx, m, n, k);
+}
+
+extern "C" int32_t rb_rope_attention_decode(rb_ctx* ctx, const void* qkv, const float* acc, int32_t n_acc, const void* bias,
+                                            const float* cos_t, const float* sin_t, int32_t rot, int32_t batch,
+                                            int32_t q_heads, rb_kv_cache* c, int32_t layer, float scale, void* q_scratch,
+                                            void* out, int32_t dtype) {
+  RB_REQUIRE(ctx && c && out && cos_t && sin_t && q_scratch, "rb_rope_attention_decode: null argument");
+  RB_REQUIRE(qkv || (acc && n_acc > 0), "rb_rope_attention_decode: no input given");
+  RB_REQUIRE(dtype == c->dtype, "rb_rope_attention_decode: cache dtype differs");
+  RB_REQUIRE(layer >= 0 && layer < c->layers, "rb_rope_attention_decode: layer %d out of range", layer);
+  RB_REQUIRE(batch > 0 && batch <= c->max_batch, "rb_rope_attention_decode: bad batch");
+  RB_REQUIRE(q_heads > 0 && q_heads % c->kv_heads == 0, "rb_rope_attention_decode: %d query heads over %d KV heads", q_heads,
+             c->kv_heads);
+  RB_REQUIRE(rot >= 0 && rot <= c->head_dim && (rot % 2) == 0, "rb_rope_attention_decode: bad rotary dim %d", rot);
+  for (int b = 0; b < batch; ++b)
+    RB_REQUIRE(c->host_lens[b] >= 1, "rb_rope_attention_decode: sequence %d is empty (its length must already count the new token)", b);
+  if (!acc) n_acc = 0;
+  const bool fused = dtype == RB_BF16 && !ctx->debug_simple_attn && !ctx->debug_no_fuse &&
+                     attention_can_fuse_rope(c, q_heads, rot, qkv, acc, n_acc, bias, cos_t, sin_t, batch);
+  if (!fused) {
+    RB_TRY(rb_rope_kv_append(ctx, qkv, acc, n_acc, bias, cos_t, sin_t, rot, batch, 1, q_heads, c, layer, q_scratch, dtype));
+    return rb_attention(ctx, q_scratch, c, layer, batch, 1, q_heads, scale, out, dtype);
+  }
+  double kv_tokens = 0.0;
+  for (int b = 0; b < batch; ++b) kv_tokens += c->host_lens[b];
+  const double d = c->head_dim, ncol = (double)(q_heads + 2 * c->kv_heads) * d;
+  ProfScope prof(ctx, RB_PROF_ATTENTION,
+                 2.0 * (2.0 * kv_tokens * c->kv_heads * d + batch * q_heads * d) + batch * ncol * ((qkv ? 2.0 : 0.0) + 4.0 * n_acc) +
+                     2.0 * batch * 2.0 * c->kv_heads * d,
+                 4.0 * kv_tokens * q_heads * d);
+  return attention_decode_fused_rope(ctx, qkv, acc, n_acc, bias, cos_t, sin_t, rot, c, layer, batch, q_heads, scale, out);
 }
 
 extern "C" int32_t rb_attention(rb_ctx* ctx, const void* q, rb_kv_cache* c, int32_t layer, int32_t batch, int32_t s_new,

@@ -91,6 +91,21 @@ struct AParams {
   float* part_o;   // [batch*q_heads][n_splits][D]
   float* part_ml;  // [batch*q_heads][n_splits][2]
   uint32_t* status;
+  // Fused single-token step (decode, tiled-copy path): the new token's q, k and v are taken straight from
+  // the q/k/v projection's output (bf16 rows and/or float32 split-K partials, plus bias), rotated, and the
+  // k/v rows appended to the cache by this kernel, which then needs no separate RoPE/append launch and
+  // can request its first K/V tiles before the projection has even finished.
+  int fuse;
+  const bf16* f_qkv;     // [batch, (q_heads + 2 kv_heads) * D] or null
+  const float* f_acc;    // [f_n_acc][batch, ...] partial sums or null
+  int f_n_acc;
+  size_t f_acc_stride;
+  const bf16* f_bias;    // [(q_heads + 2 kv_heads) * D] or null
+  const float* f_cos;    // [max_pos, rot/2]
+  const float* f_sin;
+  int f_rot, f_max_seq;
+  bf16* f_k;             // the layer's K and V pages, writable
+  bf16* f_v;
 };
 
 template <int D, bool DECODE, bool TMA>
@@ -115,7 +130,13 @@ attention_kernel(const AParams p, const __grid_constant__ CUtensorMap tm_k, cons
     ptx::tma_prefetch_desc(&tm_v);
   }
   if (TMA) __syncthreads();
-  pdl_wait();  // q and the newest K/V rows come from the kernel before this one
+  // Fused step: everything up to the first use of the projection's output runs BEFORE the wait on the
+  // previous kernel.  What it reads there is older than that kernel: the block table never changes, the
+  // sequence lengths are set by a kernel that does not release its dependents early (so it completed before
+  // anything after it started), and K/V rows of earlier tokens were written by earlier steps.  The one
+  // row that is not there yet, the new token's, is patched into the staged tile from registers below.
+  const bool fuse = DECODE && TMA && p.fuse != 0;
+  if (!fuse) pdl_wait();  // q and the newest K/V rows come from the kernel before this one
 
   int b, head, kvh, q0 = 0, split = 0;
   if (DECODE) {
@@ -138,23 +159,12 @@ attention_kernel(const AParams p, const __grid_constant__ CUtensorMap tm_k, cons
     tile_lo = 0;
     tile_hi = (min(base + q0 + 64, len) + kTile - 1) / kTile;
   }
-
-  // ---- stage Q (rows beyond the valid range are zero)
-  {
-    constexpr int chunks_per_row = D / 8;
-    for (int i = threadIdx.x; i < C::kQRows * chunks_per_row; i += blockDim.x) {
-      const int r = i / chunks_per_row, c = i % chunks_per_row;
-      const bf16* src = nullptr;
-      if (DECODE) {
-        if (r < p.group) src = p.q + ((size_t)b * p.q_heads + head + r) * D + c * 8;
-      } else {
-        if (q0 + r < p.s_new) src = p.q + (((size_t)b * p.s_new + q0 + r) * p.q_heads + head) * D + c * 8;
-      }
-      const uint32_t dst = s_u32(q_s + r * C::kRowBytes + c * 16);
-      if (src) cp_async16(dst, src);
-      else *reinterpret_cast<uint4*>(q_s + r * C::kRowBytes + c * 16) = make_uint4(0, 0, 0, 0);
-    }
+  if (fuse && (len < 1 || len > p.f_max_seq)) {  // the same guard the separate RoPE/append kernel has
+    if (threadIdx.x == 0) { p.status[0] = (uint32_t)(-RB_ERR_INVALID); p.status[1] = 0x20BEu; p.status[2] = (uint32_t)(len - 1); }
+    pdl_wait();
+    return;
   }
+
   int armed_it[C::kStages];  // thread 0: iteration whose tile was last requested into each stage
 #pragma unroll
   for (int s = 0; s < C::kStages; ++s) armed_it[s] = -1;
@@ -193,11 +203,106 @@ attention_kernel(const AParams p, const __grid_constant__ CUtensorMap tm_k, cons
     if (TMA) return (dc >> 6) * (kTile * 128) + key * 128 + ((((dc & 63) >> 3) ^ (key & 7)) << 4);
     return key * C::kRowBytes + dc * 2;
   };
-  // prologue: Q + the first kStages-1 tiles, one commit group each
+
+  // the new token's tile and slot, and whether this block is the one that walks it (fused step)
+  const int new_tile = (len - 1) / kTile, new_slot = (len - 1) % kTile;
+  const bool owns_new = fuse && new_tile >= tile_lo && new_tile < tile_hi;
+  __shared__ __align__(16) bf16 new_kv[(DECODE && TMA) ? 2 * D : 8];  // the new token's k row, then its v row
+
+  if (fuse) {
+    if constexpr (DECODE && TMA) {
+      // first tiles on their way before the projection's output exists
 #pragma unroll
-  for (int s = 0; s < C::kStages - 1; ++s) {
-    if (tile_lo + s < tile_hi) load_tile(tile_lo + s, s);
-    cp_async_commit();
+      for (int s = 0; s < C::kStages - 1; ++s)
+        if (tile_lo + s < tile_hi) load_tile(tile_lo + s, s);
+      pdl_wait();
+      // q heads of this KV head, its k head and its v head out of the projection's row of this sequence
+      const int ncol = (p.q_heads + 2 * p.kv_heads) * D;
+      const size_t row = (size_t)b * ncol;
+      const int pos = len - 1;
+      const int half = p.f_rot >> 1;
+      const int pair_items = half >> 3, pass_items = (D - p.f_rot) >> 3;
+      const int per_rot_head = pair_items + pass_items;
+      const int rot_items = (p.group + 1) * per_rot_head;  // q heads, then the k head
+      const int total = rot_items + (D >> 3);
+      auto gather = [&](int col, float* v) {  // same order of additions as the separate kernel
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.f;
+        float t8[8];
+        if (p.f_qkv) { load8(p.f_qkv + row + col, t8);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] += t8[i]; }
+        for (int k = 0; k < p.f_n_acc; ++k) { load8(p.f_acc + (size_t)k * p.f_acc_stride + row + col, t8);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] += t8[i]; }
+        if (p.f_bias) { load8(p.f_bias + col, t8);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] += t8[i]; }
+      };
+      const int page = p.block_table[(size_t)b * p.pages_per_seq + new_tile];
+      const size_t new_row = (((size_t)page * p.kv_heads + kvh) * kTile + new_slot) * D;
+      // r < group: query head r of this group; r == group: the k head; r == group + 1: the v head
+      auto emit = [&](int r, int lane0, const float* v) {
+        if (r < p.group) { store8(reinterpret_cast<bf16*>(q_s + r * C::kRowBytes) + lane0, v); return; }
+        bf16* stash = new_kv + (r - p.group) * D + lane0;
+        store8(stash, v);
+        if (owns_new) *reinterpret_cast<uint4*>((r == p.group ? p.f_k : p.f_v) + new_row + lane0) = *reinterpret_cast<const uint4*>(stash);
+      };
+      for (int it = threadIdx.x; it < total; it += blockDim.x) {
+        if (it < rot_items) {
+          const int r = it / per_rot_head, j = it % per_rot_head;
+          const int col0 = (r < p.group ? head + r : p.q_heads + kvh) * D;
+          if (j < pair_items) {
+            const int i0 = j * 8;
+            float lo[8], hi[8], cs[8], sn[8], ylo[8], yhi[8];
+            gather(col0 + i0, lo);
+            gather(col0 + i0 + half, hi);
+            load8(p.f_cos + (size_t)pos * half + i0, cs);
+            load8(p.f_sin + (size_t)pos * half + i0, sn);
+            rope_rotate8(lo, hi, cs, sn, ylo, yhi);
+            emit(r, i0, ylo);
+            emit(r, i0 + half, yhi);
+          } else {
+            const int i0 = p.f_rot + (j - pair_items) * 8;
+            float v[8];
+            gather(col0 + i0, v);
+            emit(r, i0, v);
+          }
+        } else {
+          const int i0 = (it - rot_items) * 8;
+          float v[8];
+          gather((p.q_heads + p.kv_heads + kvh) * D + i0, v);
+          emit(p.group + 1, i0, v);
+        }
+      }
+      // unused query rows of the 16-row tile are zero
+      constexpr int chunks_per_row = D / 8;
+      for (int i = threadIdx.x; i < (C::kQRows - p.group) * chunks_per_row; i += blockDim.x) {
+        const int r = p.group + i / chunks_per_row, c = i % chunks_per_row;
+        *reinterpret_cast<uint4*>(q_s + r * C::kRowBytes + c * 16) = make_uint4(0, 0, 0, 0);
+      }
+    }
+  } else {
+    // ---- stage Q (rows beyond the valid range are zero)
+    constexpr int chunks_per_row = D / 8;
+    for (int i = threadIdx.x; i < C::kQRows * chunks_per_row; i += blockDim.x) {
+      const int r = i / chunks_per_row, c = i % chunks_per_row;
+      const bf16* src = nullptr;
+      if (DECODE) {
+        if (r < p.group) src = p.q + ((size_t)b * p.q_heads + head + r) * D + c * 8;
+      } else {
+        if (q0 + r < p.s_new) src = p.q + (((size_t)b * p.s_new + q0 + r) * p.q_heads + head) * D + c * 8;
+      }
+      const uint32_t dst = s_u32(q_s + r * C::kRowBytes + c * 16);
+      if (src) cp_async16(dst, src);
+      else *reinterpret_cast<uint4*>(q_s + r * C::kRowBytes + c * 16) = make_uint4(0, 0, 0, 0);
+    }
+    // prologue: Q + the first kStages-1 tiles, one commit group each
+#pragma unroll
+    for (int s = 0; s < C::kStages - 1; ++s) {
+      if (tile_lo + s < tile_hi) load_tile(tile_lo + s, s);
+      cp_async_commit();
+    }
   }
 
   const int qrow0 = DECODE ? 0 : warp * 16;  // first Q row (inside the CTA tile) of this warp
@@ -225,6 +330,16 @@ attention_kernel(const AParams p, const __grid_constant__ CUtensorMap tm_k, cons
       if (it == 0) cp_async_wait<0>();  // Q
       const bool mine = ptx::mbar_wait(&full_bar[it % C::kStages], (uint32_t)(it / C::kStages) & 1u, &abort_flag);
       if (!__syncthreads_and(mine)) { aborted = true; break; }  // uniform decision: nobody computes on a tile that never came
+      if (owns_new && tile == new_tile) {
+        // the copy of this tile may predate the new token's row: put the row in place from the block's own copy
+        uint8_t* ks_w = kv_s + (it % C::kStages) * C::kStageBytes;
+        for (int i = threadIdx.x; i < 2 * (D / 8); i += blockDim.x) {
+          const int is_v = i / (D / 8), c = i % (D / 8);
+          *reinterpret_cast<uint4*>(ks_w + is_v * C::kTileBytes + tile_off(new_slot, c * 8)) =
+              *reinterpret_cast<const uint4*>(new_kv + is_v * D + c * 8);
+        }
+        __syncthreads();
+      }
     } else {
       cp_async_wait<C::kStages - 1>();
       __syncthreads();
@@ -558,6 +673,58 @@ int attention_mma_bf16(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, in
   }
   return fail(RB_ERR_UNIMPLEMENTED, "attention: head_dim %d has no tensor-core kernel (64, 80, 96, 128, 256)",
               c->head_dim);
+}
+
+bool attention_can_fuse_rope(const rb_kv_cache* c, int q_heads, int rot, const void* qkv, const float* acc, int n_acc,
+                             const void* bias, const float* cos_t, const float* sin_t, int batch) {
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const int d = c->head_dim;
+  if (c->dtype != RB_BF16 || (d % 64) != 0 || d > 256) return false;
+  if (rot < 0 || rot > d || (rot % 16) != 0 || ((d - rot) % 8) != 0) return false;
+  if (q_heads % c->kv_heads != 0 || q_heads / c->kv_heads > 16) return false;
+  const size_t acc_stride = (size_t)batch * (q_heads + 2 * c->kv_heads) * d;
+  return al16(qkv) && al16(acc) && al16(bias) && al16(cos_t) && al16(sin_t) && ((acc_stride * sizeof(float)) % 16) == 0 &&
+         (qkv || (acc && n_acc > 0));
+}
+
+int attention_decode_fused_rope(rb_ctx* ctx, const void* qkv, const float* acc, int n_acc, const void* bias,
+                                const float* cos_t, const float* sin_t, int rot, rb_kv_cache* c, int layer, int batch,
+                                int q_heads, float scale, void* out) {
+  AParams p{};
+  const size_t loff = (size_t)layer * c->layer_stride_elems();
+  p.q = nullptr;
+  p.k = (const bf16*)c->k + loff;
+  p.v = (const bf16*)c->v + loff;
+  p.block_table = c->block_table;
+  p.seq_lens = c->seq_lens;
+  p.pages_per_seq = c->pages_per_seq;
+  p.s_new = 1;
+  p.q_heads = q_heads;
+  p.kv_heads = c->kv_heads;
+  p.group = q_heads / c->kv_heads;
+  p.scale_log2 = scale * kLog2e;
+  p.out = (bf16*)out;
+  p.status = ctx->status_dev;
+  p.fuse = 1;
+  p.f_qkv = (const bf16*)qkv;
+  p.f_acc = n_acc > 0 ? acc : nullptr;
+  p.f_n_acc = acc ? n_acc : 0;
+  p.f_acc_stride = (size_t)batch * (q_heads + 2 * c->kv_heads) * c->head_dim;
+  p.f_bias = (const bf16*)bias;
+  p.f_cos = cos_t;
+  p.f_sin = sin_t;
+  p.f_rot = rot;
+  p.f_max_seq = c->max_seq;
+  p.f_k = (bf16*)c->k + loff;
+  p.f_v = (bf16*)c->v + loff;
+  int max_len = 0;
+  for (int b = 0; b < batch; ++b) max_len = std::max(max_len, c->host_lens[b]);
+  switch (c->head_dim) {
+    case 64: return launch_attention<64>(ctx, c, p, batch, max_len);
+    case 128: return launch_attention<128>(ctx, c, p, batch, max_len);
+    case 256: return launch_attention<256>(ctx, c, p, batch, max_len);
+  }
+  return fail(RB_ERR_UNIMPLEMENTED, "fused rope + attention: head_dim %d unsupported (64, 128, 256)", c->head_dim);
 }
 
 }  // namespace rb

@@ -98,6 +98,41 @@ template <> struct Cvt<double> {
   __device__ __forceinline__ static double from_f(float v) { return (double)v; }
 };
 
+// 8 consecutive elements as float32 (16-byte accesses for bf16, two for float32)
+__device__ __forceinline__ void load8(const float* p, float* v) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* v) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void store8(float* p, const float* v) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float* v) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+// x*cos + rotate_half(x)*sin for 8 lanes of the first half (lo, partner -hi) and the 8 matching lanes of
+// the second half (hi, partner lo) of a rotary block (rai-models/src/llm/qwen2.rs:33-38,63-71).  Written
+// with explicit fused multiply-adds so that every kernel that rotates produces the same bits.
+__device__ __forceinline__ void rope_rotate8(const float* lo, const float* hi, const float* cs, const float* sn,
+                                             float* ylo, float* yhi) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    ylo[i] = __fmaf_rn(lo[i], cs[i], -__fmul_rn(hi[i], sn[i]));
+    yhi[i] = __fmaf_rn(hi[i], cs[i], __fmul_rn(lo[i], sn[i]));
+  }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -23,6 +23,7 @@ struct rb_ctx {
   unsigned long long* argmax_best = nullptr;
   unsigned int* argmax_count = nullptr;
   bool debug_simple = false;
+  bool debug_no_fuse = false;  // RAI_B200_FUSE_ROPE=0
   bool debug_simple_gemm = false, debug_simple_attn = false;  // RAI_B200_SIMPLE_GEMM / _ATTN: one kernel family only  // RAI_B200_SIMPLE=1: route bf16 through the plain kernels (debugging aid)
   // Optional per-launch timing (rb_profile_start / rb_profile_read): an event pair around each launch.
   struct ProfRec { int cls; cudaEvent_t a, b; double bytes, flops; };
@@ -112,6 +113,13 @@ int norm_tp(rb_ctx* ctx, const TpPeers& tp, int kind, const void* x, const void*
 // decoder_kernels.cu: out[r, j] = act(sum_s part[s][r][j] + bias[j]) (* sum_s part[s][r][j + n_out] when gated)
 int act_from_partials(rb_ctx* ctx, const float* part, int n_split, int64_t rows, int64_t n_all, int64_t n_out, bool gated,
                       const void* bias, int act, void* out);
+// Single-token step with the RoPE / KV-append work folded into the decode attention kernel (bf16 caches,
+// head sizes that are multiples of 64).  `attention_can_fuse_rope` says whether the shapes and pointers allow it.
+bool attention_can_fuse_rope(const rb_kv_cache* c, int q_heads, int rot, const void* qkv, const float* acc, int n_acc,
+                             const void* bias, const float* cos_t, const float* sin_t, int batch);
+int attention_decode_fused_rope(rb_ctx* ctx, const void* qkv, const float* acc, int n_acc, const void* bias,
+                                const float* cos_t, const float* sin_t, int rot, rb_kv_cache* c, int layer, int batch,
+                                int q_heads, float scale, void* out);
 int attention_decode_splits(rb_ctx* ctx, int batch, int kv_heads, int max_len);
 int attention_simple(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, int batch, int s_new, int q_heads,
                      float scale, void* out, int dtype);

@@ -101,27 +101,6 @@ __global__ void norm_kernel(int kind, const T* __restrict__ x, const T* __restri
 // 8 elements per thread-chunk, at most kChunks chunks per thread held in registers: every load of
 // the row (inputs, residual, all split-K slabs, bias) is in flight at once, which is what matters at
 // decode where only `rows` blocks exist and the kernel is pure latency.
-__device__ __forceinline__ void load8(const float* p, float* v) {
-  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
-  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
-__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* v) {
-  const uint4 u = *reinterpret_cast<const uint4*>(p);
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
-}
-__device__ __forceinline__ void store8(float* p, const float* v) {
-  reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
-  reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
-}
-__device__ __forceinline__ void store8(__nv_bfloat16* p, const float* v) {
-  uint4 u;
-  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-  *reinterpret_cast<uint4*>(p) = u;
-}
 template <typename T>
 __device__ __forceinline__ void round_to(float* v) {
 #pragma unroll
@@ -469,11 +448,7 @@ __global__ void rope_kv_append_vec_kernel(const T* __restrict__ qkv, const float
         gather(head * d + i0 + half, hi);
         load8(cos_t + (size_t)pos * half + i0, cs);
         load8(sin_t + (size_t)pos * half + i0, sn);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          ylo[i] = lo[i] * cs[i] - hi[i] * sn[i];  // x*cos + rotate_half(x)*sin, first half: partner is -x[i+half]
-          yhi[i] = hi[i] * cs[i] + lo[i] * sn[i];  // second half: partner is x[i-half]
-        }
+        rope_rotate8(lo, hi, cs, sn, ylo, yhi);
         emit(head, i0, ylo);
         emit(head, i0 + half, yhi);
       } else {

@@ -353,14 +353,25 @@ int forward_body(rb_model* m, const uint32_t* tokens, int batch, int seq, void* 
     int s = 1;
     if (use_partials(m, rows, m->nqkv_l, H, &s)) {
       RB_TRY(rb_linear_partials(ctx, m->xn, w.qkv, m->scratch, rows, m->nqkv_l, H, s));
-      RB_TRY(rb_rope_kv_append(ctx, nullptr, m->scratch, s, w.qkv_b, m->rope_cos, m->rope_sin, c.rotary_dim, batch, seq,
-                               m->nq_l, m->cache, l, m->q, c.dtype));
+      if (seq == 1) {  // single-token step: RoPE and the cache append ride in the attention kernel when they can
+        RB_TRY(rb_rope_attention_decode(ctx, nullptr, m->scratch, s, w.qkv_b, m->rope_cos, m->rope_sin, c.rotary_dim, batch,
+                                        m->nq_l, m->cache, l, scale, m->q, m->attn, c.dtype));
+      } else {
+        RB_TRY(rb_rope_kv_append(ctx, nullptr, m->scratch, s, w.qkv_b, m->rope_cos, m->rope_sin, c.rotary_dim, batch, seq,
+                                 m->nq_l, m->cache, l, m->q, c.dtype));
+        RB_TRY(rb_attention(ctx, m->q, m->cache, l, batch, seq, m->nq_l, scale, m->attn, c.dtype));
+      }
     } else {
       RB_TRY(rb_linear(ctx, m->xn, w.qkv, w.qkv_b, nullptr, m->qkv, rows, m->nqkv_l, H, RB_ACT_NONE, c.dtype));
-      RB_TRY(rb_rope_kv_append(ctx, m->qkv, nullptr, 0, nullptr, m->rope_cos, m->rope_sin, c.rotary_dim, batch, seq,
-                               m->nq_l, m->cache, l, m->q, c.dtype));
+      if (seq == 1) {
+        RB_TRY(rb_rope_attention_decode(ctx, m->qkv, nullptr, 0, nullptr, m->rope_cos, m->rope_sin, c.rotary_dim, batch,
+                                        m->nq_l, m->cache, l, scale, m->q, m->attn, c.dtype));
+      } else {
+        RB_TRY(rb_rope_kv_append(ctx, m->qkv, nullptr, 0, nullptr, m->rope_cos, m->rope_sin, c.rotary_dim, batch, seq,
+                                 m->nq_l, m->cache, l, m->q, c.dtype));
+        RB_TRY(rb_attention(ctx, m->q, m->cache, l, batch, seq, m->nq_l, scale, m->attn, c.dtype));
+      }
     }
-    RB_TRY(rb_attention(ctx, m->q, m->cache, l, batch, seq, m->nq_l, scale, m->attn, c.dtype));
     RB_TRY(linear_into_residual(m, pend, m->attn, w.o, w.o_b, rows, H, (int64_t)m->nq_l * d));
     if (c.arch == RB_ARCH_PHI2) {
       // parallel block (phi2.rs:293-299): the MLP reads the same normed input as the attention.
