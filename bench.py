@@ -216,7 +216,7 @@ def decode_timeline(model, dev, rewind, first, T0, path, steps=4):
     t0 = evs[0].time_range.start
     seq, by_name, prev_end = [], {}, None
     for e in evs:
-        name = e.name.split("(")[0].replace("void ", "").replace("rb::", "").replace("(anonymous namespace)::", "")
+        name = e.name.replace("(anonymous namespace)::", "").replace("void ", "").replace("rb::", "").split("(")[0]
         start, end = e.time_range.start - t0, e.time_range.end - t0
         gap = None if prev_end is None else start - prev_end
         prev_end = end if prev_end is None else max(prev_end, end)
@@ -477,7 +477,7 @@ def run_ours(args):
         "achieved": gemm.get("achieved_gbs"), "peak": peaks["hbm_gbs"] * world, "unit": "GB/s",
         "frac": (gemm["achieved_gbs"] / (peaks["hbm_gbs"] * world)) if gemm.get("achieved_gbs") else None,
         "peak_kind": f"{peak_kind} stream-copy bandwidth x {world} GPU(s)",
-        # DRAM bytes per launch: ncu (profiles/gemm_tc_decode_2layer_b64.md) measured 476.7 MB of DRAM
+        # DRAM bytes per launch: ncu (profiles/gemm_tc_decode_2layer_b64.md) measured 478.6 MB of DRAM
         # read+write for the four GEMMs of one layer against 486.2 MB of algorithmic bytes (the float32
         # split-K partials mostly stay in L2), i.e. 0.98 of algorithmic; scaled to this run's launches.
         "traffic": (0.98 * gemm["gbytes_per_step"] * 1e9 / gemm["launches_per_step"]) if gemm else None,
