@@ -5,8 +5,9 @@ Names follow the derive rule of rai-core/src/nn.rs:256-269 (field path joined by
 phi3.rs:260-266 and gemma.rs:309-318, i.e. the keys of a Hugging Face safetensors checkpoint.
 
 Synthetic weights stand in for real checkpoints (none are available offline): every Linear and
-Embedding matrix ~ N(0, 0.02), biases ~ N(0, 0.02), norm weights 1 (0 for gemma, whose norm applies
-1 + w), LayerNorm biases 0; token ids uniform on [0, vocab).
+Embedding matrix ~ N(0, 0.02), biases ~ N(0, 0.02), norm weights 1 + N(0, 0.05) (0 + N(0, 0.05) for
+gemma, whose norm applies 1 + w; the noise keeps a kernel that forgets the weight from passing), LayerNorm
+biases ~ N(0, 0.02); token ids uniform on [0, vocab).
 """
 from __future__ import annotations
 
