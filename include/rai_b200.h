@@ -319,13 +319,27 @@ int32_t rb_tp_unique_id(void* out128);
  * position only.  logits_dev may be NULL. */
 int32_t rb_model_forward(rb_model* m, const uint32_t* tokens_dev, int32_t batch, int32_t seq, int32_t pos,
                          void* logits_dev);
+/* Model::fwd for a right-padded batch: sequence b has lens_host[b] (1..seq) valid tokens, then padding.
+ * Logits come from each sequence's last valid position and the cache keeps lens_host[b] tokens of
+ * sequence b, so later single-token calls continue every sequence at its own length.  The reference has
+ * no counterpart: its batches are rectangular (qwen2.rs:340-351 builds one mask for all rows) and its
+ * examples run one sequence; a server batching prompts of different lengths needs this. */
+int32_t rb_model_forward_ragged(rb_model* m, const uint32_t* tokens_dev, int32_t batch, int32_t seq, int32_t pos,
+                                const int32_t* lens_host, void* logits_dev);
+/* rb_model_generate_step for the prompts of a right-padded batch, from an empty cache: host tokens
+ * [batch, seq] and lens_host in, one sampled token per sequence out.  Synchronous.  Continue with
+ * rb_model_generate_step / rb_model_decode_loop passing pos = -1 ("each sequence at its own length"). */
+int32_t rb_model_generate_ragged(rb_model* m, const uint32_t* tokens_host, int32_t batch, int32_t seq,
+                                 const int32_t* lens_host, uint32_t* next_host);
 /* One iteration of the generation loop (examples/qwen2/src/main.rs:78-91) with greedy sampling:
  * host tokens in (pinned memory recommended) -> H2D -> forward -> on-device argmax -> D2H of
- * batch u32 token ids.  Synchronous. */
+ * batch u32 token ids.  Synchronous.  pos is the reference's seqlen_offset and must equal the cached
+ * length; pos = -1 with seq == 1 continues every sequence at its own cached length. */
 int32_t rb_model_generate_step(rb_model* m, const uint32_t* tokens_host, int32_t batch, int32_t seq, int32_t pos,
                                uint32_t* next_host);
 /* Decode loop kept on the device: `steps` greedy single-token steps starting from tokens_dev
- * [batch] at position pos; writes out_dev [steps, batch].  Asynchronous. */
+ * [batch] at position pos (or -1: each sequence at its own cached length); writes out_dev [steps, batch].
+ * Asynchronous. */
 int32_t rb_model_decode_loop(rb_model* m, const uint32_t* tokens_dev, int32_t batch, int32_t pos, int32_t steps,
                              uint32_t* out_dev);
 /* Sampling used by rb_model_generate_step and rb_model_decode_loop, as in the examples' loops

@@ -115,14 +115,23 @@ __global__ void advance_lens_kernel(int32_t* lens, int n, int delta) {
 // entries per sequence are ever read (`tokens[start_at..]`, main.rs:86-87): a ring per sequence, written at
 // (count + s) % cap.  Membership is all the penalty needs, so the order inside the ring is irrelevant.
 __global__ void history_push_kernel(const uint32_t* __restrict__ ids, int batch, int seq, int32_t* __restrict__ hist,
-                                    int32_t* __restrict__ count, int cap) {
+                                    int32_t* __restrict__ count, int cap, const int32_t* __restrict__ last_rows) {
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= batch) return;
   const int c = count[b];
-  for (int s = max(0, seq - cap); s < seq; ++s) hist[(size_t)b * cap + (c + s) % cap] = (int32_t)ids[(size_t)b * seq + s];
-  int n = c + seq;
+  const int valid = last_rows ? last_rows[b] - b * seq + 1 : seq;  // right-padded batch: pads are not part of the text
+  for (int s = max(0, valid - cap); s < valid; ++s) hist[(size_t)b * cap + (c + s) % cap] = (int32_t)ids[(size_t)b * seq + s];
+  int n = c + valid;
   if (n >= 2 * cap) n = cap + n % cap;  // same slot arithmetic, still "full", and bounded
   count[b] = n;
+}
+
+// dst[b, :] = src[rows[b], :]  (16-byte pieces; the last valid position of every sequence of a ragged batch)
+__global__ void gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ rows, uint4* __restrict__ dst,
+                                   int pieces_per_row) {
+  const int b = blockIdx.x;
+  const size_t r = (size_t)rows[b];
+  for (int i = threadIdx.x; i < pieces_per_row; i += blockDim.x) dst[(size_t)b * pieces_per_row + i] = src[r * pieces_per_row + i];
 }
 
 // out[b, r*vl + j] = gathered[r, b, j]  (vocabulary shards back into rows of logits)
@@ -168,6 +177,8 @@ struct rb_model {
   void *h = nullptr, *xn = nullptr, *tmp = nullptr, *qkv = nullptr, *q = nullptr, *attn = nullptr, *act = nullptr;
   void *last_h = nullptr, *logits = nullptr, *logits_g = nullptr;
   uint32_t* next_ids = nullptr;
+  int32_t* last_rows = nullptr;           // ragged prefill: row of each sequence's last valid token
+  std::vector<int32_t> last_rows_host;    // outlives the asynchronous upload
   float* scratch = nullptr;  // split-K partials
   size_t scratch_floats = 0;
   void* comm = nullptr;
@@ -287,7 +298,7 @@ int linear_into_residual(rb_model* m, Pending& pend, const void* x, const void* 
   return rb_linear(m->ctx, x, w, b, m->h, m->h, rows, n, k, RB_ACT_NONE, m->cfg.dtype);
 }
 
-int forward_body(rb_model* m, const uint32_t* tokens, int batch, int seq, void* logits_out);
+int forward_body(rb_model* m, const uint32_t* tokens, int batch, int seq, void* logits_out, const int32_t* last_rows = nullptr);
 
 // act = activation(x . W1^T [+ b1]) [* (x . Wup^T)]  -- the first half of MLP::fwd.  When the fused kernel
 // would leave most SMs idle (decode-sized rows and few 128-row weight tiles, i.e. small or sharded
@@ -333,7 +344,7 @@ int forward_impl(rb_model* m, const uint32_t* tokens, int batch, int seq, int po
 
 // The launches of one forward pass.  Everything position-dependent is read from device memory (the
 // cache's sequence lengths), so the same sequence of launches serves every decode step.
-int forward_body(rb_model* m, const uint32_t* tokens, int batch, int seq, void* logits_out) {
+int forward_body(rb_model* m, const uint32_t* tokens, int batch, int seq, void* logits_out, const int32_t* last_rows) {
   const rb_model_config& c = m->cfg;
   rb_ctx* ctx = m->ctx;
   const int64_t rows = (int64_t)batch * seq;
@@ -389,7 +400,13 @@ int forward_body(rb_model* m, const uint32_t* tokens, int batch, int seq, void* 
   // logits for the last position only (qwen2.rs:356-358; phi2.rs:345-346 normalises every row first,
   // which is the same thing for a row-wise norm)
   const void* last = m->h;
-  if (seq > 1) {
+  if (seq > 1 && last_rows) {
+    RB_REQUIRE(((size_t)H * m->es) % 16 == 0, "ragged forward: hidden rows must be multiples of 16 bytes");
+    gather_rows_kernel<<<batch, 128, 0, ctx->stream>>>((const uint4*)m->h, last_rows, (uint4*)m->last_h, (int)((size_t)H * m->es / 16));
+    RB_CUDA(cudaGetLastError());
+    ctx->launches++;
+    last = m->last_h;
+  } else if (seq > 1) {
     RB_CUDA(cudaMemcpy2DAsync(m->last_h, (size_t)H * m->es, (const char*)m->h + (size_t)(seq - 1) * H * m->es,
                               (size_t)seq * H * m->es, (size_t)H * m->es, batch, cudaMemcpyDeviceToDevice, ctx->stream));
     last = m->last_h;
@@ -674,6 +691,7 @@ extern "C" int32_t rb_model_create(rb_ctx* ctx, const rb_model_config* cfg, rb_m
   W((size_t)c.max_batch * V * m->es, &m->logits);
   if (tp > 1) W((size_t)c.max_batch * Vl * m->es * (tp + 1), &m->logits_g);
   W((size_t)c.max_batch * sizeof(uint32_t), (void**)&m->next_ids);
+  W((size_t)c.max_batch * sizeof(int32_t), (void**)&m->last_rows);
   if (c.dtype == RB_BF16) {
     // split-K scratch: up to 16 slabs of min(max_tokens, 256) rows of the widest split-K output
     const size_t rows = std::min<size_t>(MT, 256);
@@ -952,6 +970,42 @@ extern "C" int32_t rb_model_finished(rb_model* m, int32_t batch, uint8_t* flags_
   return RB_OK;
 }
 
+// Right-padded batch: sequence b has lens[b] valid tokens followed by padding.  The rectangle runs as usual
+// (under the causal mask a pad can only influence later pads), the logits come from each sequence's last
+// valid row, and the cache keeps lens[b] tokens of sequence b: the pads' K/V rows lie beyond that length,
+// are never read, and are overwritten by the tokens decoded next.
+static int forward_ragged(rb_model* m, const uint32_t* tokens, int batch, int seq, int pos, const int32_t* lens, void* logits_out) {
+  rb_ctx* ctx = m->ctx;
+  rb_kv_cache* kc = m->cache;
+  for (int b = 0; b < batch; ++b)
+    RB_REQUIRE(lens[b] >= 1 && lens[b] <= seq, "ragged forward: sequence %d has %d valid tokens of %d", b, lens[b], seq);
+  m->last_rows_host.assign((size_t)batch, 0);
+  for (int b = 0; b < batch; ++b) m->last_rows_host[b] = b * seq + lens[b] - 1;
+  RB_CUDA(cudaMemcpyAsync(m->last_rows, m->last_rows_host.data(), (size_t)batch * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+  const rb_model_config& c = m->cfg;
+  const int64_t rows = (int64_t)batch * seq;
+  RB_REQUIRE(batch > 0 && batch <= c.max_batch, "forward: batch %d exceeds max_batch %d", batch, c.max_batch);
+  RB_REQUIRE(seq > 0 && rows <= c.max_tokens, "forward: %lld tokens exceed max_tokens %d", (long long)rows, c.max_tokens);
+  RB_REQUIRE(pos >= 0 && pos + seq <= kc->max_seq && pos + seq <= c.max_position_embeddings,
+             "forward: position %d + %d exceeds the cache / rotary table capacity", pos, seq);
+  for (int b = 0; b < batch; ++b)
+    RB_REQUIRE(kc->host_lens[b] == pos, "forward: seqlen_offset %d differs from the cached length %d of sequence %d", pos,
+               kc->host_lens[b], b);
+  set_lens_kernel<<<(batch + 127) / 128, 128, 0, ctx->stream>>>(kc->seq_lens, batch, pos + seq);
+  ctx->launches++;
+  for (int b = 0; b < batch; ++b) kc->host_lens[b] = pos + seq;
+  RB_TRY(forward_body(m, tokens, batch, seq, logits_out, seq > 1 ? m->last_rows : nullptr));
+  for (int b = 0; b < batch; ++b) kc->host_lens[b] = pos + lens[b];
+  RB_CUDA(cudaMemcpyAsync(kc->seq_lens, kc->host_lens.data(), (size_t)batch * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+  return RB_OK;
+}
+
+extern "C" int32_t rb_model_forward_ragged(rb_model* m, const uint32_t* tokens_dev, int32_t batch, int32_t seq, int32_t pos,
+                                           const int32_t* lens_host, void* logits_dev) {
+  RB_REQUIRE(m && tokens_dev && lens_host, "rb_model_forward_ragged: null argument");
+  return forward_ragged(m, tokens_dev, batch, seq, pos, lens_host, logits_dev);
+}
+
 extern "C" int32_t rb_model_forward(rb_model* m, const uint32_t* tokens_dev, int32_t batch, int32_t seq, int32_t pos,
                                     void* logits_dev) {
   RB_REQUIRE(m && tokens_dev, "rb_model_forward: null argument");
@@ -972,9 +1026,10 @@ int sampling_reset(rb_model* m) {
 
 // The tokens about to be fed join the history BEFORE the sampling that follows their forward pass: at
 // that point the examples' `tokens` holds the prompt and every token generated so far (main.rs:84-92).
-int history_push(rb_model* m, const uint32_t* ids, int batch, int seq) {
+int history_push(rb_model* m, const uint32_t* ids, int batch, int seq, const int32_t* last_rows = nullptr) {
   if (!(m->rep_penalty >= 1.0f && m->rep_last_n > 0)) return RB_OK;
-  history_push_kernel<<<(batch + 127) / 128, 128, 0, m->ctx->stream>>>(ids, batch, seq, m->hist, m->hist_count, m->rep_last_n);
+  history_push_kernel<<<(batch + 127) / 128, 128, 0, m->ctx->stream>>>(ids, batch, seq, m->hist, m->hist_count, m->rep_last_n,
+                                                                      last_rows);
   RB_CUDA(cudaGetLastError());
   m->ctx->launches++;
   return RB_OK;
@@ -1011,12 +1066,11 @@ int decode_step(rb_model* m, int batch) {
   rb_ctx* ctx = m->ctx;
   rb_kv_cache* c = m->cache;
   RB_REQUIRE(batch > 0 && batch <= m->cfg.max_batch, "decode: batch %d exceeds max_batch %d", batch, m->cfg.max_batch);
-  const int len0 = c->host_lens[0];
-  RB_REQUIRE(len0 + 1 <= c->max_seq && len0 + 1 <= m->cfg.max_position_embeddings,
-             "decode: position %d exceeds the cache / rotary table capacity", len0);
+  // every sequence continues at its own cached length (they differ after a ragged prefill)
   for (int b = 0; b < batch; ++b)
-    RB_REQUIRE(c->host_lens[b] == len0, "decode: sequences of one batch must have equal lengths");
-  for (int b = 0; b < batch; ++b) c->host_lens[b] = len0 + 1;
+    RB_REQUIRE(c->host_lens[b] + 1 <= c->max_seq && c->host_lens[b] + 1 <= m->cfg.max_position_embeddings,
+               "decode: position %d of sequence %d exceeds the cache / rotary table capacity", c->host_lens[b], b);
+  for (int b = 0; b < batch; ++b) c->host_lens[b] += 1;
   const int plan = decode_plan(m, batch);
   const bool graphable = m->use_graph && m->cfg.dtype == RB_BF16 && !ctx->profiling && !ctx->debug_simple;
   if (graphable && m->step_graph && m->graph_batch == batch && m->graph_plan == plan) {
@@ -1096,7 +1150,8 @@ extern "C" int32_t rb_model_generate_step(rb_model* m, const uint32_t* tokens_ho
   RB_REQUIRE(batch > 0 && seq > 0 && (int64_t)batch * seq <= m->cfg.max_tokens, "rb_model_generate_step: bad sizes");
   rb_ctx* ctx = m->ctx;
   const bool single = seq == 1 && !ctx->profiling;
-  if (single)
+  RB_REQUIRE(pos >= 0 || seq == 1, "generate_step: a negative seqlen_offset (own lengths) needs single-token steps");
+  if (single && pos >= 0)
     for (int b = 0; b < batch; ++b)
       RB_REQUIRE(m->cache->host_lens[b] == pos, "generate_step: seqlen_offset %d differs from the cached length %d", pos,
                  m->cache->host_lens[b]);
@@ -1107,8 +1162,14 @@ extern "C" int32_t rb_model_generate_step(rb_model* m, const uint32_t* tokens_ho
     if (single) {
       RB_TRY(decode_step(m, batch));
     } else {
+      int at = pos;
+      if (at < 0) {  // own lengths, plain launches (profiling): they must agree for a rectangular forward
+        at = m->cache->host_lens[0];
+        for (int b = 0; b < batch; ++b)
+          RB_REQUIRE(m->cache->host_lens[b] == at, "generate_step: sequences of different lengths cannot be profiled launch by launch");
+      }
       RB_TRY(history_push(m, m->ids, batch, seq));
-      RB_TRY(forward_impl(m, m->ids, batch, seq, pos, nullptr));
+      RB_TRY(forward_impl(m, m->ids, batch, seq, at, nullptr));
       RB_TRY(sample_tokens(m, batch, m->next_ids));
       result = m->next_ids;
     }
@@ -1120,13 +1181,34 @@ extern "C" int32_t rb_model_generate_step(rb_model* m, const uint32_t* tokens_ho
   return rb_sync(ctx);
 }
 
+extern "C" int32_t rb_model_generate_ragged(rb_model* m, const uint32_t* tokens_host, int32_t batch, int32_t seq,
+                                            const int32_t* lens_host, uint32_t* next_host) {
+  RB_REQUIRE(m && tokens_host && lens_host && next_host, "rb_model_generate_ragged: null argument");
+  RB_REQUIRE(batch > 0 && seq > 0 && (int64_t)batch * seq <= m->cfg.max_tokens, "rb_model_generate_ragged: bad sizes");
+  rb_ctx* ctx = m->ctx;
+  const int st = on_own_stream(m, [&]() -> int {
+    RB_CUDA(cudaMemcpyAsync(m->ids, tokens_host, (size_t)batch * seq * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream));
+    RB_TRY(sampling_reset(m));
+    RB_TRY(forward_ragged(m, m->ids, batch, seq, 0, lens_host, nullptr));
+    // the history takes each sequence's valid tokens only (last_rows was uploaded by forward_ragged)
+    RB_TRY(history_push(m, m->ids, batch, seq, seq > 1 ? m->last_rows : nullptr));
+    RB_TRY(sample_tokens(m, batch, m->next_ids));
+    RB_CUDA(cudaMemcpyAsync(next_host, m->next_ids, (size_t)batch * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+    return RB_OK;
+  });
+  RB_TRY(st);
+  RB_CUDA(cudaStreamSynchronize(ctx->own_stream));
+  return rb_sync(ctx);
+}
+
 extern "C" int32_t rb_model_decode_loop(rb_model* m, const uint32_t* tokens_dev, int32_t batch, int32_t pos,
                                         int32_t steps, uint32_t* out_dev) {
   RB_REQUIRE(m && tokens_dev && out_dev, "rb_model_decode_loop: null argument");
   RB_REQUIRE(batch > 0 && batch <= m->cfg.max_batch && steps >= 0, "rb_model_decode_loop: bad sizes");
-  for (int b = 0; b < batch; ++b)
-    RB_REQUIRE(m->cache->host_lens[b] == pos, "decode_loop: seqlen_offset %d differs from the cached length %d", pos,
-               m->cache->host_lens[b]);
+  if (pos >= 0)
+    for (int b = 0; b < batch; ++b)
+      RB_REQUIRE(m->cache->host_lens[b] == pos, "decode_loop: seqlen_offset %d differs from the cached length %d", pos,
+                 m->cache->host_lens[b]);
   rb_ctx* ctx = m->ctx;
   auto body = [&]() -> int {
     RB_CUDA(cudaMemcpyAsync(m->ids, tokens_dev, (size_t)batch * sizeof(uint32_t), cudaMemcpyDeviceToDevice, ctx->stream));

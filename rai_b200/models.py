@@ -105,6 +105,40 @@ class Model:
         self.device.synchronize()
         return logits if self.cfg["arch"] == "phi2" else logits.unsqueeze(1)
 
+    def forward_ragged(self, tokens, lens, seqlen_offset: int = 0) -> torch.Tensor:
+        """Model::fwd for a right-padded batch: tokens [B, S], lens[b] valid tokens in row b.  Logits [B, V] of each
+        sequence's last valid position; the cache keeps lens[b] tokens of sequence b."""
+        ids = self._tokens_dev(tokens)
+        b, s = ids.shape
+        lens_arr = np.ascontiguousarray(np.asarray(lens, dtype=np.int32))
+        self.device.use_torch_stream()
+        logits = torch.empty((b, self.cfg["vocab_size"]), dtype=_TORCH_DTYPE[self.dtype], device=ids.device)
+        _lib.call("rb_model_forward_ragged", self._m, ctypes.c_void_p(ids.data_ptr()), b, s, int(seqlen_offset),
+                  lens_arr.ctypes.data_as(ctypes.c_void_p), ctypes.c_void_p(logits.data_ptr()))
+        self.device.synchronize()
+        return logits
+
+    def generate_ragged(self, prompts, steps: int) -> np.ndarray:
+        """Generation for prompts of different lengths in one batch (a list of 1-D token arrays): right-pad, one
+        ragged prompt call, then the device-side decode loop with every sequence at its own length.  [B, steps]."""
+        b = len(prompts)
+        lens = np.asarray([len(p) for p in prompts], dtype=np.int32)
+        s = int(lens.max())
+        ids = np.zeros((b, s), dtype=np.int32)
+        for i, p in enumerate(prompts):
+            ids[i, : len(p)] = np.asarray(p, dtype=np.int32)
+        tok_in = torch.from_numpy(ids).pin_memory()
+        first = torch.empty((b,), dtype=torch.int32).pin_memory()
+        self.clear_kv_cache()
+        _lib.call("rb_model_generate_ragged", self._m, ctypes.c_void_p(tok_in.data_ptr()), b, s,
+                  lens.ctypes.data_as(ctypes.c_void_p), ctypes.c_void_p(first.data_ptr()))
+        out = [first.numpy().astype(np.int64).reshape(b, 1)]
+        if steps > 1:
+            rest = self.decode_loop(first.to(f"cuda:{self.device.id}"), -1, steps - 1)
+            self.device.synchronize()
+            out.append(rest.cpu().numpy().astype(np.int64).T)
+        return np.concatenate(out, axis=1)
+
     def generate_step(self, tokens_host: torch.Tensor, seqlen_offset: int, out_host: torch.Tensor) -> None:
         """One iteration of the examples' generation loop with greedy sampling on the device:
         tokens_host [B, S] int32 (pinned) -> out_host [B] int32 (pinned).  Synchronous."""
