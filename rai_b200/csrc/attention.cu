@@ -232,9 +232,7 @@ attention_kernel(const AParams p, const __grid_constant__ CUtensorMap tm_k, cons
         if (p.f_qkv) { load8(p.f_qkv + row + col, t8);
 #pragma unroll
           for (int i = 0; i < 8; ++i) v[i] += t8[i]; }
-        for (int k = 0; k < p.f_n_acc; ++k) { load8(p.f_acc + (size_t)k * p.f_acc_stride + row + col, t8);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) v[i] += t8[i]; }
+        add_slabs<4>(p.f_acc, p.f_n_acc, p.f_acc_stride, row + col, v);
         if (p.f_bias) { load8(p.f_bias + col, t8);
 #pragma unroll
           for (int i = 0; i < 8; ++i) v[i] += t8[i]; }

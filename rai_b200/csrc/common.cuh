@@ -121,6 +121,25 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float* v) {
   *reinterpret_cast<uint4*>(p) = u;
 }
 
+// v[i] += slab_0[i] + slab_1[i] + ... in slab order (so the result does not depend on how the loads are
+// scheduled), with the loads of up to G slabs issued before the first sum needs them: one memory round trip
+// per group instead of one per slab.
+template <int G = 8>
+__device__ __forceinline__ void add_slabs(const float* __restrict__ acc, int n_acc, size_t stride, size_t off, float* v) {
+  for (int k0 = 0; k0 < n_acc; k0 += G) {
+    float t[G][8];
+#pragma unroll
+    for (int k = 0; k < G; ++k)
+      if (k0 + k < n_acc) load8(acc + (size_t)(k0 + k) * stride + off, t[k]);
+#pragma unroll
+    for (int k = 0; k < G; ++k)
+      if (k0 + k < n_acc) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] += t[k][i];
+      }
+  }
+}
+
 // x*cos + rotate_half(x)*sin for 8 lanes of the first half (lo, partner -hi) and the 8 matching lanes of
 // the second half (hi, partner lo) of a rotary block (rai-models/src/llm/qwen2.rs:33-38,63-71).  Written
 // with explicit fused multiply-adds so that every kernel that rotates produces the same bits.

@@ -127,7 +127,7 @@ __device__ __forceinline__ void load8_sys(const __nv_bfloat16* p, float* v) {
 __device__ __forceinline__ void load8_sys(const float* p, float* v) { load8(p, v); }  // exchange buffers are bf16 only
 
 template <typename T, int kChunks, bool TP>
-__global__ void norm_vec_kernel(int kind, const T* __restrict__ x, const T* __restrict__ add,
+__global__ void __launch_bounds__(512) norm_vec_kernel(int kind, const T* __restrict__ x, const T* __restrict__ add,
                                 const float* __restrict__ acc, int n_acc, size_t acc_stride,
                                 const T* __restrict__ acc_bias, const T* __restrict__ w, const T* __restrict__ b,
                                 float eps, int hidden, T* __restrict__ out, T* __restrict__ sum_out, const TpPeers tp,
@@ -187,9 +187,7 @@ __global__ void norm_vec_kernel(int kind, const T* __restrict__ x, const T* __re
     if (add) { load8(add + base + ch * 8, t);
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[c][i] += t[i]; }
-    for (int k = 0; k < n_acc; ++k) { load8(acc + (size_t)k * acc_stride + base + ch * 8, t);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) v[c][i] += t[i]; }
+    add_slabs(acc, n_acc, acc_stride, base + ch * 8, v[c]);
     if (acc_bias) { load8(acc_bias + ch * 8, t);
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[c][i] += t[i]; }
@@ -252,7 +250,7 @@ __global__ void norm_vec_kernel(int kind, const T* __restrict__ x, const T* __re
 // goes into the next slot of its exchange buffer; the last block to finish bumps the sequence number
 // and raises this rank's flag in every peer's flag array.
 template <typename T>
-__global__ void tp_publish_kernel(const float* __restrict__ acc, int n_acc, size_t acc_stride, const T* __restrict__ bias,
+__global__ void __launch_bounds__(512) tp_publish_kernel(const float* __restrict__ acc, int n_acc, size_t acc_stride, const T* __restrict__ bias,
                                   const T* __restrict__ x, int hidden, const TpPeers tp) {
   __shared__ uint32_t last_block;
   pdl_launch_dependents();
@@ -265,9 +263,7 @@ __global__ void tp_publish_kernel(const float* __restrict__ acc, int n_acc, size
     if (x) { load8(x + base + ch * 8, t);
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[i] += t[i]; }
-    for (int k = 0; k < n_acc; ++k) { load8(acc + (size_t)k * acc_stride + base + ch * 8, t);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] += t[i]; }
+    add_slabs(acc, n_acc, acc_stride, base + ch * 8, v);
     if (bias) { load8(bias + ch * 8, t);
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[i] += t[i]; }
