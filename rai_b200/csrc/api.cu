@@ -200,6 +200,7 @@ extern "C" int32_t rb_kv_cache_create(rb_ctx* ctx, int32_t layers, int32_t kv_he
   if (st == RB_OK) st = rb_malloc(ctx, bytes, &c->v);
   if (st == RB_OK) st = rb_malloc(ctx, (size_t)c->num_pages * sizeof(int32_t), (void**)&c->block_table);
   if (st == RB_OK) st = rb_malloc(ctx, (size_t)max_batch * sizeof(int32_t), (void**)&c->seq_lens);
+  if (st == RB_OK) st = rb_malloc(ctx, (size_t)max_batch * kv_heads * sizeof(uint32_t), (void**)&c->split_count);
   if (st != RB_OK) { rb_kv_cache_destroy(c); return st; }
   // Zero the pages: the tail of a sequence's last page is read (and masked) by the attention
   // kernels, so it must hold finite values.
@@ -209,6 +210,7 @@ extern "C" int32_t rb_kv_cache_create(rb_ctx* ctx, int32_t layers, int32_t kv_he
   for (int i = 0; i < c->num_pages; ++i) bt[i] = i;  // sequence b owns pages [b*pages_per_seq, ...)
   RB_CUDA(cudaMemcpyAsync(c->block_table, bt.data(), bt.size() * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
   RB_CUDA(cudaMemsetAsync(c->seq_lens, 0, (size_t)max_batch * sizeof(int32_t), ctx->stream));
+  RB_CUDA(cudaMemsetAsync(c->split_count, 0, (size_t)max_batch * kv_heads * sizeof(uint32_t), ctx->stream));
   RB_CUDA(cudaStreamSynchronize(ctx->stream));
   c->host_lens.assign(max_batch, 0);
   *out = c;
@@ -222,6 +224,7 @@ extern "C" int32_t rb_kv_cache_destroy(rb_kv_cache* c) {
   if (c->v) cudaFree(c->v);
   if (c->block_table) cudaFree(c->block_table);
   if (c->seq_lens) cudaFree(c->seq_lens);
+  if (c->split_count) cudaFree(c->split_count);
   delete c;
   return RB_OK;
 }

@@ -90,6 +90,7 @@ struct AParams {
   bf16* out;
   float* part_o;   // [batch*q_heads][n_splits][D]
   float* part_ml;  // [batch*q_heads][n_splits][2]
+  uint32_t* split_count;  // [batch][kv_heads] arrivals; non-null: the last split block of a (sequence, KV head) merges
   uint32_t* status;
   // Fused single-token step (decode, tiled-copy path): the new token's q, k and v are taken straight from
   // the q/k/v projection's output (bf16 rows and/or float32 split-K partials, plus bias), rotated, and the
@@ -496,6 +497,34 @@ attention_kernel(const AParams p, const __grid_constant__ CUtensorMap tm_k, cons
       if (dd == 0) { p.part_ml[(bh * p.n_splits + split) * 2] = M; p.part_ml[(bh * p.n_splits + split) * 2 + 1] = L; }
     }
   }
+  if (p.n_splits == 1 || !p.split_count) return;
+  // The split block that arrives last for this (sequence, KV head) merges all of them: same sums, in the
+  // same split order, as attention_merge_kernel, without the extra launch.
+  __shared__ uint32_t is_last;
+  __threadfence();   // this block's partials are visible device-wide before it is counted
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t* cnt = p.split_count + (size_t)b * p.kv_heads + kvh;
+    const uint32_t arrived = atomicAdd(cnt, 1u);
+    is_last = (arrived == (uint32_t)p.n_splits - 1u) ? 1u : 0u;
+    if (is_last) *cnt = 0u;  // re-armed for the next launch (which starts after this grid has completed)
+    __threadfence();
+  }
+  __syncthreads();
+  if (!is_last) return;
+  for (int idx = threadIdx.x; idx < p.group * D; idx += blockDim.x) {
+    const int row = idx / D, dd = idx % D;
+    const size_t bh = (size_t)b * p.q_heads + head + row;
+    const float* ml_p = p.part_ml + bh * p.n_splits * 2;
+    const float* o_p = p.part_o + bh * p.n_splits * D;
+    float M = -INFINITY;
+    for (int sp = 0; sp < p.n_splits; ++sp) M = fmaxf(M, __ldcg(ml_p + sp * 2));
+    const float Mu = (M == -INFINITY) ? 0.f : M;
+    float L = 0.f, O = 0.f;
+    for (int sp = 0; sp < p.n_splits; ++sp) L += __ldcg(ml_p + sp * 2 + 1) * exp2f(__ldcg(ml_p + sp * 2) - Mu);
+    for (int sp = 0; sp < p.n_splits; ++sp) O += __ldcg(o_p + (size_t)sp * D + dd) * exp2f(__ldcg(ml_p + sp * 2) - Mu);
+    p.out[bh * D + dd] = __float2bfloat16_rn(O / L);
+  }
 }
 
 // Merges the per-split (max, sum, O) of the decode kernel: one block per (sequence, head).
@@ -571,8 +600,10 @@ int launch_attention(rb_ctx* ctx, rb_kv_cache* c, AParams& p, int batch, int max
     p.part_ml = sc.ptr + (size_t)batch * p.q_heads * splits * D;
   }
   dim3 grid((unsigned)splits, (unsigned)p.kv_heads, (unsigned)batch);
+  static const bool separate_merge = getenv("RAI_B200_ATTN_MERGE_KERNEL") != nullptr;  // debugging aid
+  p.split_count = (splits > 1 && !separate_merge) ? c->split_count : nullptr;
   RB_TRY((launch_attn_kernel<D, true>(ctx, c, p, grid)));
-  if (splits > 1) {
+  if (splits > 1 && !p.split_count) {
     RB_CUDA(launch_kernel(attention_merge_kernel, dim3((unsigned)(batch * p.q_heads)), dim3(128), 0, ctx->stream, ctx->pdl,
                           (const float*)p.part_o, (const float*)p.part_ml, splits, D, p.out));
     ctx->launches++;

@@ -40,6 +40,7 @@ struct rb_kv_cache {
   void* v = nullptr;
   int32_t* block_table = nullptr;  // device [max_batch][pages_per_seq]
   int32_t* seq_lens = nullptr;     // device [max_batch]
+  uint32_t* split_count = nullptr;  // device [max_batch][kv_heads]: arrivals of a split decode attention; self-resetting
   std::vector<int32_t> host_lens;
   size_t layer_stride_elems() const { return (size_t)num_pages * kv_heads * 64 * head_dim; }
 };
