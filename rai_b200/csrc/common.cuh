@@ -121,6 +121,14 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float* v) {
   *reinterpret_cast<uint4*>(p) = u;
 }
 
+__device__ __forceinline__ uint4 pack8_bf16(const float* v) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  return u;
+}
+
 // v[i] += slab_0[i] + slab_1[i] + ... in slab order (so the result does not depend on how the loads are
 // scheduled), with the loads of up to G slabs issued before the first sum needs them: one memory round trip
 // per group instead of one per slab.

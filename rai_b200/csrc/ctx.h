@@ -45,15 +45,15 @@ struct rb_kv_cache {
   size_t layer_stride_elems() const { return (size_t)num_pages * kv_heads * 64 * head_dim; }
 };
 
-// Peer-memory exchange of a tensor-parallel group for decode-sized allreduces: every rank publishes
-// its partial [rows, hidden] in its own exchange buffer and raises a flag in every peer's flag
-// array; the consumer waits (bounded) for all flags and sums the peers' buffers in rank order while
-// it reads them over NVLink ("reduce on read").  Two slots, chosen by the parity of a device-side
-// sequence number, so replayed CUDA graphs need no new arguments.
+// Peer-memory exchange of a tensor-parallel group for decode-sized allreduces: every rank pushes its
+// partial [rows, hidden] into its own place in EVERY rank's exchange buffer (posted stores over NVLink,
+// no round trip) and then raises a flag in every peer's flag array; the consumer waits (bounded) for
+// all flags and sums the copies in its own memory in rank order, the same on every rank.  Two slots,
+// chosen by the parity of a device-side sequence number, so replayed CUDA graphs need no new arguments.
 constexpr int kTpMaxRanks = 8;
 constexpr int kTpMaxRows = 256;
 struct TpPeers {
-  const void* xbuf[kTpMaxRanks];   // every rank's exchange buffer (own included), [2][kTpMaxRows][hidden]
+  const void* xbuf[kTpMaxRanks];   // every rank's exchange buffer (own included), [2 slots][size sources][kTpMaxRows][hidden]
   uint32_t* flags[kTpMaxRanks];    // every rank's flag array, [2][kTpMaxRanks]
   uint32_t* seq;                   // local: number of exchanges published so far
   uint32_t* block_count;           // local: arrival counter of the publishing kernel

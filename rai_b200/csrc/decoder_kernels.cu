@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(512) norm_vec_kernel(int kind, const T* __rest
     __syncthreads();
     if (tp_seq_s == 0xffffffffu) return;  // a peer never arrived: leave the outputs alone, the host sees the status
     // thread 0's acquire loads plus the barrier order every thread's (system-scope) reads below behind the flags
-    tp_off = (size_t)(tp_seq_s & 1u) * tp.slot_elems;
+    tp_off = (size_t)(tp_seq_s & 1u) * tp.size * tp.slot_elems;
   }
   float v[kChunks][8];
   float s = 0.f;
@@ -191,13 +191,19 @@ __global__ void __launch_bounds__(512) norm_vec_kernel(int kind, const T* __rest
     if (acc_bias) { load8(acc_bias + ch * 8, t);
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[c][i] += t[i]; }
-    if (TP) {  // the peers' partial sums, read over NVLink, added in rank order on every rank alike
+    if (TP) {  // every rank's partial sum, pushed into THIS rank's buffer by its owner, added in rank order on every rank alike
       float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int r = 0; r < tp.size; ++r) {
-        load8_sys(reinterpret_cast<const T*>(tp.xbuf[r]) + tp_off + base + ch * 8, t);
+      const T* mine = reinterpret_cast<const T*>(tp.xbuf[tp.rank]) + tp_off + base + ch * 8;
+      float pr[kTpMaxRanks][8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sum[i] += t[i];
-      }
+      for (int r = 0; r < kTpMaxRanks; ++r)
+        if (r < tp.size) load8_sys(mine + (size_t)r * tp.slot_elems, pr[r]);
+#pragma unroll
+      for (int r = 0; r < kTpMaxRanks; ++r)
+        if (r < tp.size) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sum[i] += pr[r][i];
+        }
       round_to<T>(sum);  // what an allreduce in the model dtype would have delivered
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[c][i] += sum[i];
@@ -256,7 +262,8 @@ __global__ void __launch_bounds__(512) tp_publish_kernel(const float* __restrict
   pdl_launch_dependents();
   pdl_wait();
   const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(tp.seq) + 1u;
-  T* dst = reinterpret_cast<T*>(const_cast<void*>(tp.xbuf[tp.rank])) + (size_t)(seq & 1u) * tp.slot_elems;
+  // slot (seq & 1), source `rank`, inside every rank's buffer: [2 slots][size sources][rows x hidden]
+  const size_t dst_off = ((size_t)(seq & 1u) * tp.size + tp.rank) * tp.slot_elems;
   const size_t base = (size_t)blockIdx.x * hidden;
   for (int ch = threadIdx.x; ch < (hidden >> 3); ch += blockDim.x) {
     float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, t[8];
@@ -267,11 +274,16 @@ __global__ void __launch_bounds__(512) tp_publish_kernel(const float* __restrict
     if (bias) { load8(bias + ch * 8, t);
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[i] += t[i]; }
-    store8(dst + base + ch * 8, v);
+    // the same 16 bytes into every rank's copy: posted stores over NVLink, nobody waits for a reply
+    const uint4 packed = pack8_bf16(v);
+#pragma unroll
+    for (int r = 0; r < kTpMaxRanks; ++r)
+      if (r < tp.size)
+        *reinterpret_cast<uint4*>(reinterpret_cast<T*>(const_cast<void*>(tp.xbuf[r])) + dst_off + base + ch * 8) = packed;
   }
   __syncthreads();  // the block's stores are ordered before thread 0's fence (cumulativity through the barrier)
   if (threadIdx.x == 0) {
-    __threadfence();
+    __threadfence_system();  // this block's stores to the peers are performed before it is counted
     const unsigned int arrived = atomicAdd(tp.block_count, 1u);
     last_block = (arrived == gridDim.x - 1) ? 1u : 0u;
     if (last_block) {

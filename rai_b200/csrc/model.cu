@@ -327,7 +327,6 @@ int forward_impl(rb_model* m, const uint32_t* tokens, int batch, int seq, int po
   const rb_model_config& c = m->cfg;
   rb_ctx* ctx = m->ctx;
   const int64_t rows = (int64_t)batch * seq;
-  const int H = c.hidden_size, d = m->d;
   RB_REQUIRE(batch > 0 && batch <= c.max_batch, "forward: batch %d exceeds max_batch %d", batch, c.max_batch);
   RB_REQUIRE(seq > 0 && rows <= c.max_tokens, "forward: %lld tokens exceed max_tokens %d", (long long)rows, c.max_tokens);
   RB_REQUIRE(pos >= 0 && pos + seq <= m->cache->max_seq && pos + seq <= c.max_position_embeddings,
@@ -469,7 +468,7 @@ extern "C" int32_t rb_model_tp_init(rb_model* m, const void* id, int32_t id_byte
   rb_ctx* ctx = m->ctx;
   const int tp = m->cfg.tp_size, rank = m->cfg.tp_rank;
   const size_t slot_elems = (size_t)kTpMaxRows * m->cfg.hidden_size;
-  const size_t bytes = 256 + 2 * slot_elems * 2;
+  const size_t bytes = 256 + 2 * (size_t)tp * slot_elems * 2;  // header, then [2 slots][tp sources][rows x hidden] bf16
   RB_TRY(rb_malloc(ctx, bytes, &m->xchg_base));
   m->owned.push_back(m->xchg_base);
   RB_CUDA(cudaMemsetAsync(m->xchg_base, 0, bytes, ctx->stream));
