@@ -116,7 +116,8 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// 16 bytes of a peer's exchange buffer, read at system scope so that no stale L1 line can serve it
+// 16 bytes of this rank's exchange buffer, which its peers write over NVLink: read at system scope so that no
+// stale L1 line can serve it
 __device__ __forceinline__ void load8_sys(const __nv_bfloat16* p, float* v) {
   uint4 u;
   asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "l"(p) : "memory");
@@ -253,8 +254,8 @@ __global__ void __launch_bounds__(512) norm_vec_kernel(int kind, const T* __rest
 
 
 // Tensor-parallel publish: this rank's partial product (split-K slabs + bias, or a finished tensor x)
-// goes into the next slot of its exchange buffer; the last block to finish bumps the sequence number
-// and raises this rank's flag in every peer's flag array.
+// is pushed into this rank's place of the next slot in EVERY rank's exchange buffer; the last block to
+// finish bumps the sequence number and raises this rank's flag in every peer's flag array.
 template <typename T>
 __global__ void __launch_bounds__(512) tp_publish_kernel(const float* __restrict__ acc, int n_acc, size_t acc_stride, const T* __restrict__ bias,
                                   const T* __restrict__ x, int hidden, const TpPeers tp) {
