@@ -21,6 +21,7 @@ import numpy as np
 import torch
 
 from . import _lib
+from . import shape as _shape
 from .device import Cuda
 
 _TORCH = {_lib.F32: torch.float32, _lib.BF16: torch.bfloat16, _lib.U32: torch.int32, _lib.U8: torch.uint8}
@@ -58,10 +59,10 @@ def _dense_strides(shape: Sequence[int]) -> List[int]:
 
 def _resolve_dim(dim: int, rank: int) -> int:
     """Negative dims count from the end (rai-core/src/dim.rs:7-104)."""
-    d = dim + rank if dim < 0 else dim
-    if not 0 <= d < rank:
+    try:
+        return _shape.dim([0] * rank, dim)
+    except IndexError:
         raise _lib.RaiB200Error(-2, f"dim {dim} out of range for rank {rank}")
-    return d
 
 
 class Tensor:
@@ -326,7 +327,10 @@ def _matmul(a: Tensor, b: Tensor) -> Tensor:
     k2, n = b.shape[-2], b.shape[-1]
     if k != k2:
         raise _lib.RaiB200Error(-2, f"matmul of {a.shape} and {b.shape}")
-    batch_shape = list(np.broadcast_shapes(tuple(a.shape[:-2]), tuple(b.shape[:-2])))
+    try:
+        batch_shape = _shape.broadcast_matmul(a.shape, b.shape)[0][:-2]   # shape.rs:129-160
+    except ValueError as e:
+        raise _lib.RaiB200Error(-2, str(e))
     batch = int(np.prod(batch_shape)) if batch_shape else 1
     # Linear's `weight.broadcast_left(batch).t()` (linear.rs:59-69): B is a broadcast, transposed [n, k] matrix
     b_is_linear = b.strides[-1] == k and b.strides[-2] == 1 and all(s == 0 for s in b.strides[:-2])
