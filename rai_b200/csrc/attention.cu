@@ -146,7 +146,8 @@ attention_kernel(const AParams p, const __grid_constant__ CUtensorMap tm_k, cons
     q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * 64;  // longest causal ranges first
     head = blockIdx.y; b = blockIdx.z; kvh = head / p.group;
   }
-  const int len = p.seq_lens[b];
+  // (fused step: read before the dependency wait, so straight from L2, where the kernel that set it left it)
+  const int len = fuse ? __ldcg(p.seq_lens + b) : p.seq_lens[b];
   const int base = len - p.s_new;  // absolute position of query row 0
 
   // key tiles this CTA walks
