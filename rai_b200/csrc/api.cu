@@ -88,6 +88,7 @@ extern "C" int32_t rb_destroy(rb_ctx* ctx) {
   if (ctx->status_dev) cudaFree(ctx->status_dev);
   if (ctx->argmax_best) cudaFree(ctx->argmax_best);
   if (ctx->argmax_count) cudaFree(ctx->argmax_count);
+  if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
   delete ctx;
   return RB_OK;

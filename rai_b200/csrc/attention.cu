@@ -553,8 +553,9 @@ int launch_attn_kernel(rb_ctx* ctx, rb_kv_cache* c, const AParams& p, dim3 grid)
   constexpr bool kTma = (D % 64) == 0;
   using C = ACfg<D, DECODE, kTma>;
   auto kern = attention_kernel<D, DECODE, kTma>;
-  static bool set = false;
-  if (!set) { RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes)); set = true; }
+  static bool set[64] = {};  // the attribute belongs to the (kernel, device) pair
+  const int dv = ctx->device & 63;
+  if (!set[dv]) { RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes)); set[dv] = true; }
   CUtensorMap none{};
   const CUtensorMap *tk = &none, *tv = &none;
   if (kTma) {
@@ -566,15 +567,6 @@ int launch_attn_kernel(rb_ctx* ctx, rb_kv_cache* c, const AParams& p, dim3 grid)
   RB_CUDA(launch_kernel(kern, grid, dim3(128), (size_t)C::kSmemBytes, ctx->stream, ctx->pdl, p, *tk, *tv));
   ctx->launches++;
   return RB_OK;
-}
-
-struct Scratch {
-  float* ptr = nullptr;
-  size_t bytes = 0;
-};
-std::map<int, Scratch>& scratch_by_device() {
-  static std::map<int, Scratch> m;
-  return m;
 }
 
 template <int D>
@@ -590,15 +582,15 @@ int launch_attention(rb_ctx* ctx, rb_kv_cache* c, AParams& p, int batch, int max
   p.n_splits = splits;
   if (splits > 1) {
     const size_t need = (size_t)batch * p.q_heads * splits * (D + 2) * sizeof(float);
-    Scratch& sc = scratch_by_device()[ctx->device];
-    if (sc.bytes < need) {
-      if (sc.ptr) RB_CUDA(cudaFree(sc.ptr));
-      sc.ptr = nullptr; sc.bytes = 0;
-      RB_CUDA(cudaMalloc(&sc.ptr, need));
-      sc.bytes = need;
+    if (ctx->attn_scratch_bytes < need) {
+      // cudaFree waits for the kernels that may still read the old buffer
+      if (ctx->attn_scratch) RB_CUDA(cudaFree(ctx->attn_scratch));
+      ctx->attn_scratch = nullptr; ctx->attn_scratch_bytes = 0;
+      RB_CUDA(cudaMalloc(&ctx->attn_scratch, need));
+      ctx->attn_scratch_bytes = need;
     }
-    p.part_o = sc.ptr;
-    p.part_ml = sc.ptr + (size_t)batch * p.q_heads * splits * D;
+    p.part_o = ctx->attn_scratch;
+    p.part_ml = ctx->attn_scratch + (size_t)batch * p.q_heads * splits * D;
   }
   dim3 grid((unsigned)splits, (unsigned)p.kv_heads, (unsigned)batch);
   static const bool separate_merge = getenv("RAI_B200_ATTN_MERGE_KERNEL") != nullptr;  // debugging aid

@@ -22,6 +22,9 @@ struct rb_ctx {
   // argmax across blocks: running best (key << 32 | index) and arrival count per row; self-resetting
   unsigned long long* argmax_best = nullptr;
   unsigned int* argmax_count = nullptr;
+  // split-KV partials of the decode attention: grown on demand, owned by the context (one stream at a time)
+  float* attn_scratch = nullptr;
+  size_t attn_scratch_bytes = 0;
   bool debug_simple = false;
   bool debug_no_fuse = false;  // RAI_B200_FUSE_ROPE=0
   bool debug_simple_gemm = false, debug_simple_attn = false;  // RAI_B200_SIMPLE_GEMM / _ATTN: one kernel family only  // RAI_B200_SIMPLE=1: route bf16 through the plain kernels (debugging aid)

@@ -512,10 +512,11 @@ int launch(rb_ctx* ctx, const GemmArgs& a, Params& p) {
   p.n_q = (p.q_rows + BN - 1) / BN;
   p.n_items = p.n_p * p.n_q * p.n_split;
   auto kern = gemm_tc_kernel<BN, SWAP, GATED>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[64] = {};  // the attribute belongs to the (kernel, device) pair
+  const int dv = ctx->device & 63;
+  if (!attr_set[dv]) {
     RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
-    attr_set = true;
+    attr_set[dv] = true;
   }
   const int grid = std::min(p.n_items, ctx->sm_count);
   static const bool trace = getenv("RAI_B200_GEMM_TRACE") != nullptr;
