@@ -11,6 +11,11 @@ for p in (ROOT, os.path.join(ROOT, "oracle"), os.path.dirname(os.path.abspath(__
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a B200; run with `-m gpu`")
+    # A fresh checkout has no built library (it is not kept in history): build it once so that the tests that
+    # only load it and check its exports can run.  Where the compiler is absent the tests fail loudly instead.
+    from rai_b200 import build as b
+    if not b.LIB.exists():
+        b.build()
 
 
 @pytest.fixture(scope="session")
