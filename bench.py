@@ -46,6 +46,7 @@ def parse_args():
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--profile-steps", type=int, default=8)
+    ap.add_argument("--skip-timeline", action="store_true")
     ap.add_argument("--timeline", default="", help="write a per-kernel device timeline of a few decode steps (as replayed, "
                     "overlap included) to this JSON file; a tracing pass of its own, never part of the timed region")
     ap.add_argument("--shard-of", type=int, default=0,
@@ -196,10 +197,12 @@ def cpu_decode_sample(cfg, batch, ctx, steps, warmup):
             "ms_per_step": step_s * 1e3}
 
 
-def decode_timeline(model, dev, rewind, first, T0, path, steps=4):
+def decode_timeline(model, dev, rewind, first, T0, path=None, steps=4):
     """Kernel start/end times of `steps` decode steps as the device ran them (graph replay, dependent launches
-    overlapping), from the CUDA activity records torch's profiler collects.  Per kernel name: launches, busy time,
-    and the idle gap between the previous kernel's end and this one's start; plus the raw sequence of one step."""
+    overlapping), from the CUDA activity records torch's profiler collects.  With dependent launches a kernel's own
+    duration includes the time it sits waiting for its predecessor, so the figure kept per kernel name is its
+    `advance`: how far it moves the end of the step (its end minus the latest end before it).  Returns the summary
+    (None when no activity records are available) and writes it, with the raw sequence of one step, to `path`."""
     import torch
     from torch.profiler import ProfilerActivity, profile
     rewind(T0)
@@ -211,26 +214,25 @@ def decode_timeline(model, dev, rewind, first, T0, path, steps=4):
     evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and e.time_range.end > e.time_range.start]
     evs.sort(key=lambda e: e.time_range.start)
     if not evs:
-        json.dump({"error": "no device activity records"}, open(path, "w"))
-        return
+        return None
     t0 = evs[0].time_range.start
     seq, by_name, prev_end = [], {}, None
     for e in evs:
         name = e.name.replace("(anonymous namespace)::", "").replace("void ", "").replace("rb::", "").split("(")[0]
         start, end = e.time_range.start - t0, e.time_range.end - t0
-        gap = None if prev_end is None else start - prev_end
+        advance = (end - start) if prev_end is None else max(0.0, end - prev_end)
         prev_end = end if prev_end is None else max(prev_end, end)
-        seq.append({"name": name, "start_us": round(start, 2), "dur_us": round(end - start, 2), "gap_us": None if gap is None else round(gap, 2)})
-        a = by_name.setdefault(name, {"launches": 0, "busy_us": 0.0, "gap_us": 0.0, "overlapped_us": 0.0})
+        seq.append({"name": name, "start_us": round(start, 2), "dur_us": round(end - start, 2), "advance_us": round(advance, 2)})
+        a = by_name.setdefault(name, {"launches": 0, "advance_us": 0.0})
         a["launches"] += 1
-        a["busy_us"] += end - start
-        if gap is not None:
-            a["gap_us" if gap >= 0 else "overlapped_us"] += abs(gap)
+        a["advance_us"] += advance
     span = max(x["start_us"] + x["dur_us"] for x in seq)
     per_step = {k: {kk: round(vv / steps, 2) for kk, vv in v.items()} for k, v in by_name.items()}
     n = len(seq) // steps
-    json.dump({"steps": steps, "span_us_per_step": round(span / steps, 1), "per_kernel_per_step": per_step,
-               "one_step": seq[n:2 * n]}, open(path, "w"), indent=1)
+    out = {"steps": steps, "span_us_per_step": round(span / steps, 1), "per_kernel_per_step": per_step}
+    if path:
+        json.dump(dict(out, one_step=seq[n:2 * n]), open(path, "w"), indent=1)
+    return out
 
 
 def run_reference(args):
@@ -397,8 +399,13 @@ def run_ours(args):
                            "achieved_gbs": out4[2] / 1e9 / (out4[1] / 1e3) if out4[1] > 0 else None}
     dev.synchronize()
 
-    if args.timeline and rank == 0:
-        decode_timeline(model, dev, rewind, first, T0, args.timeline)
+    # ---- the same steps as the device ran them (graph replay, overlap included): a tracing pass of its own
+    in_graph = None
+    if rank == 0 and not args.skip_timeline:
+        try:
+            in_graph = decode_timeline(model, dev, rewind, first, T0, args.timeline or None)
+        except Exception as e:  # tracing is an extra: the bench line does not depend on it
+            in_graph = {"error": f"{type(e).__name__}: {e}"}
 
     # ---- end to end through the generation-step call: pinned host tokens in, token ids out, per step
     e2e = None
@@ -490,6 +497,19 @@ def run_ours(args):
                        "frac_of_nominal_8tbs": step_gbs / (NOMINAL_HBM_GBS * world)},
         "per_class": prof,
     }
+    if in_graph and "per_kernel_per_step" in in_graph and gemm:
+        # The per-launch figures above time every launch alone (an event pair around it, no overlap with its
+        # neighbours).  In the replayed step consecutive kernels overlap (dependent launches, weights requested
+        # ahead of the dependency), so there the GEMMs' share of the step is their `advance`.
+        adv = sum(v["advance_us"] for k, v in in_graph["per_kernel_per_step"].items() if k.startswith("gemm_tc_kernel"))
+        roofline["in_graph"] = {
+            "method": "CUDA activity records of the replayed step; per kernel: its end minus the latest end before it",
+            "span_us_per_step": in_graph["span_us_per_step"], "gemm_advance_us_per_step": adv,
+            "gemm_achieved_gbs": (gemm["gbytes_per_step"] * 1e3 / adv) if adv > 0 else None,
+            "gemm_frac": (gemm["gbytes_per_step"] * 1e3 / adv / (peaks["hbm_gbs"] * world)) if adv > 0 else None,
+            "per_kernel_per_step": in_graph["per_kernel_per_step"]}
+    elif in_graph:
+        roofline["in_graph"] = in_graph
     if prefill:
         prefill["frac_of_measured_sustained_bf16"] = prefill["tflops"] / (peaks["bf16_tflops_sustained"] * world)
         prefill["frac_of_nominal_bf16"] = prefill["tflops"] / (NOMINAL_BF16_TFLOPS * world)
