@@ -505,8 +505,8 @@ def run_ours(args):
         roofline["in_graph"] = {
             "method": "CUDA activity records of the replayed step; per kernel: its end minus the latest end before it",
             "span_us_per_step": in_graph["span_us_per_step"], "gemm_advance_us_per_step": adv,
-            "gemm_achieved_gbs": (gemm["gbytes_per_step"] * 1e3 / adv) if adv > 0 else None,
-            "gemm_frac": (gemm["gbytes_per_step"] * 1e3 / adv / (peaks["hbm_gbs"] * world)) if adv > 0 else None,
+            "gemm_achieved_gbs": (gemm["gbytes_per_step"] * 1e6 / adv) if adv > 0 else None,
+            "gemm_frac": (gemm["gbytes_per_step"] * 1e6 / adv / (peaks["hbm_gbs"] * world)) if adv > 0 else None,
             "per_kernel_per_step": in_graph["per_kernel_per_step"]}
     elif in_graph:
         roofline["in_graph"] = in_graph
