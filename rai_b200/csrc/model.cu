@@ -1071,7 +1071,7 @@ int decode_step(rb_model* m, int batch) {
                "decode: position %d of sequence %d exceeds the cache / rotary table capacity", c->host_lens[b], b);
   for (int b = 0; b < batch; ++b) c->host_lens[b] += 1;
   const int plan = decode_plan(m, batch);
-  const bool graphable = m->use_graph && m->cfg.dtype == RB_BF16 && !ctx->profiling && !ctx->debug_simple;
+  const bool graphable = m->use_graph && !ctx->profiling && !ctx->debug_simple;
   if (graphable && m->step_graph && m->graph_batch == batch && m->graph_plan == plan) {
     RB_CUDA(cudaGraphLaunch(m->step_graph, ctx->stream));
     ctx->launches += m->graph_launches;

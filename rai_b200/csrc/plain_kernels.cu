@@ -65,16 +65,76 @@ __global__ void gemm_plain_kernel(const T* __restrict__ x, const T* __restrict__
     }
 }
 
-// One warp per (token, query head): streams the keys of the paged cache with an online softmax.
-// Lanes split head_dim; float32 throughout.  Correct for any head_dim <= 256.
+// Decode-sized float32 Linear (M <= 8 rows; the reference's examples generate with batch 1 in float32,
+// examples/qwen2/src/main.rs:58).  One warp per output feature: its weight row is read once with 16-byte loads
+// and all M dot products ride along, so the kernel is bound by the weight stream like its bf16 counterpart.
+template <bool GATED>
+__global__ void __launch_bounds__(256) gemv_f32_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                       const float* __restrict__ w2, const float* __restrict__ bias,
+                                                       const float* __restrict__ residual, float* __restrict__ out, int m,
+                                                       int n, int k, int act, int vec) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col = blockIdx.x * 8 + warp;
+  if (col >= n) return;
+  const float* wr = w + (size_t)col * k;
+  const float* wr2 = GATED ? w2 + (size_t)col * k : nullptr;
+  float acc[8], acc2[8];
+#pragma unroll
+  for (int r = 0; r < 8; ++r) { acc[r] = 0.f; acc2[r] = 0.f; }
+  if (vec) {
+    for (int i = lane * 4; i < k; i += 128) {
+      const float4 a = *reinterpret_cast<const float4*>(wr + i);
+      float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (GATED) b = *reinterpret_cast<const float4*>(wr2 + i);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (r >= m) break;
+        const float4 xv = *reinterpret_cast<const float4*>(x + (size_t)r * k + i);
+        acc[r] = fmaf(a.w, xv.w, fmaf(a.z, xv.z, fmaf(a.y, xv.y, fmaf(a.x, xv.x, acc[r]))));
+        if (GATED) acc2[r] = fmaf(b.w, xv.w, fmaf(b.z, xv.z, fmaf(b.y, xv.y, fmaf(b.x, xv.x, acc2[r]))));
+      }
+    }
+  } else {
+    for (int i = lane; i < k; i += 32) {
+      const float a = wr[i], b = GATED ? wr2[i] : 0.f;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (r >= m) break;
+        const float xv = x[(size_t)r * k + i];
+        acc[r] = fmaf(a, xv, acc[r]);
+        if (GATED) acc2[r] = fmaf(b, xv, acc2[r]);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 8; ++r) {
+    if (r >= m) break;
+    float v = warp_sum(acc[r]);
+    const float v2 = GATED ? warp_sum(acc2[r]) : 0.f;
+    if (lane != 0) continue;
+    if (GATED) {
+      v = act_apply(act, v) * v2;
+    } else {
+      if (bias) v += bias[col];
+      v = act_apply(act, v);
+      if (residual) v += residual[(size_t)r * n + col];
+    }
+    out[(size_t)r * n + col] = v;
+  }
+}
+
+// One block per (token, query head): its 8 warps take every 8th key of the paged cache, each with an online
+// softmax of its own (lanes split head_dim), and their (max, sum, O) states are merged through shared memory.
+// float32 throughout.  Correct for any head_dim <= 256.
+constexpr int kPlainAttnWarps = 8;
 template <typename T>
-__global__ void attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
-                                       const T* __restrict__ v_cache, const int32_t* __restrict__ block_table,
-                                       const int32_t* __restrict__ seq_lens, int pages_per_seq, int s_new, int q_heads,
-                                       int kv_heads, int d, float scale, T* __restrict__ out) {
-  const int m = blockIdx.x, h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (h >= q_heads) return;
-  const int lane = threadIdx.x & 31;
+__global__ void __launch_bounds__(kPlainAttnWarps * 32)
+attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                       const int32_t* __restrict__ block_table, const int32_t* __restrict__ seq_lens, int pages_per_seq,
+                       int s_new, int q_heads, int kv_heads, int d, float scale, T* __restrict__ out) {
+  __shared__ float sm_m[kPlainAttnWarps], sm_l[kPlainAttnWarps], sm_o[kPlainAttnWarps][256];
+  const int m = blockIdx.x, h = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = m / s_new, s = m % s_new;
   const int limit = seq_lens[b] - s_new + s;  // last visible key
   const int kvh = h / (q_heads / kv_heads);
@@ -86,7 +146,7 @@ __global__ void attention_plain_kernel(const T* __restrict__ q, const T* __restr
     o[j] = 0.f;
   }
   float mx = -INFINITY, l = 0.f;
-  for (int t = 0; t <= limit; ++t) {
+  for (int t = warp; t <= limit; t += kPlainAttnWarps) {
     const int page = block_table[(size_t)b * pages_per_seq + t / kPageTokens];
     const size_t off = (((size_t)page * kv_heads + kvh) * kPageTokens + (t % kPageTokens)) * d;
     float dot = 0.f;
@@ -106,11 +166,41 @@ __global__ void attention_plain_kernel(const T* __restrict__ q, const T* __restr
     }
     mx = mn;
   }
+  if (lane == 0) { sm_m[warp] = mx; sm_l[warp] = l; }
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const int i = lane + 32 * j;
-    if (i < d) out[((size_t)m * q_heads + h) * d + i] = Cvt<T>::from_f(o[j] / l);
+    if (i < d) sm_o[warp][i] = o[j];
   }
+  __syncthreads();
+  float M = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < kPlainAttnWarps; ++w) M = fmaxf(M, sm_m[w]);
+  float L = 0.f;
+#pragma unroll
+  for (int w = 0; w < kPlainAttnWarps; ++w) L += (sm_m[w] == -INFINITY) ? 0.f : sm_l[w] * expf(sm_m[w] - M);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float O = 0.f;
+#pragma unroll
+    for (int w = 0; w < kPlainAttnWarps; ++w) O += (sm_m[w] == -INFINITY) ? 0.f : sm_o[w][i] * expf(sm_m[w] - M);
+    out[((size_t)m * q_heads + h) * d + i] = Cvt<T>::from_f(O / L);
+  }
+}
+
+static bool gemv_f32_launch(rb_ctx* ctx, const GemmArgs& a) {
+  if (a.partials || a.m > 8) return false;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const int vec = (a.k % 4 == 0) && al16(a.x) && al16(a.w) && (!a.w2 || al16(a.w2));
+  const dim3 grid((unsigned)((a.n + 7) / 8));
+  if (a.w2)
+    gemv_f32_kernel<true><<<grid, 256, 0, ctx->stream>>>((const float*)a.x, (const float*)a.w, (const float*)a.w2, nullptr, nullptr,
+                                                         (float*)a.out, (int)a.m, (int)a.n, (int)a.k, a.act, vec);
+  else
+    gemv_f32_kernel<false><<<grid, 256, 0, ctx->stream>>>((const float*)a.x, (const float*)a.w, nullptr, (const float*)a.bias,
+                                                          (const float*)a.residual, (float*)a.out, (int)a.m, (int)a.n, (int)a.k,
+                                                          a.act, vec);
+  ctx->launches++;
+  return true;
 }
 
 template <typename T>
@@ -133,7 +223,10 @@ static int gemm_plain_launch(rb_ctx* ctx, const GemmArgs& a) {
 
 int gemm_simple(rb_ctx* ctx, const GemmArgs& a, int dtype) {
   if (a.m == 0 || a.n == 0) return RB_OK;
-  if (dtype == RB_F32) return gemm_plain_launch<float>(ctx, a);
+  if (dtype == RB_F32) {
+    if (gemv_f32_launch(ctx, a)) return launch_status("gemv_f32");
+    return gemm_plain_launch<float>(ctx, a);
+  }
   if (dtype == RB_BF16) return gemm_plain_launch<__nv_bfloat16>(ctx, a);
   return fail(RB_ERR_DTYPE, "gemm: dtype %d unsupported", dtype);
 }
@@ -141,8 +234,8 @@ int gemm_simple(rb_ctx* ctx, const GemmArgs& a, int dtype) {
 int attention_simple(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, int batch, int s_new, int q_heads,
                      float scale, void* out, int dtype) {
   const size_t loff = (size_t)layer * c->layer_stride_elems();
-  const int warps = 4;
-  dim3 grid((unsigned)(batch * s_new), (unsigned)((q_heads + warps - 1) / warps));
+  const int warps = kPlainAttnWarps;
+  dim3 grid((unsigned)(batch * s_new), (unsigned)q_heads);
   if (dtype == RB_F32)
     attention_plain_kernel<float><<<grid, warps * 32, 0, ctx->stream>>>(
         (const float*)q, (const float*)c->k + loff, (const float*)c->v + loff, c->block_table, c->seq_lens,
