@@ -91,6 +91,13 @@ int32_t rb_sm_count(rb_ctx* ctx);
 /* Device memory owned by the library (`TensorLike` storage, rai-core/src/tensor.rs:19-26). */
 int32_t rb_malloc(rb_ctx* ctx, size_t bytes, void** out_dev);
 int32_t rb_free(rb_ctx* ctx, void* dev);
+/* The same pair, stream-ordered and pooled (cudaMallocAsync / cudaFreeAsync on the context's stream): what a
+ * binding uses for the output of every primitive, where the reference's rules let candle allocate
+ * (candle.rs:197-1004) and drop storage with the last Rc (tensor.rs:34).  Neither call synchronises; a block
+ * freed here may be handed out again by a later rb_malloc_async and is safe to reuse in stream order.  Not
+ * for memory that is shared between processes (use rb_malloc). */
+int32_t rb_malloc_async(rb_ctx* ctx, size_t bytes, void** out_dev);
+int32_t rb_free_async(rb_ctx* ctx, void* dev);
 /* ToDevice<Cuda> on Cpu data / ToDevice<Cpu> on Cuda data (rai-core/src/backend/candle.rs:776-790).
  * rb_download synchronises the stream. */
 int32_t rb_upload(rb_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);

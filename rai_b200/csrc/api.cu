@@ -158,6 +158,38 @@ extern "C" int32_t rb_malloc(rb_ctx* ctx, size_t bytes, void** out) {
   return RB_OK;
 }
 
+// Stream-ordered allocation from the device's memory pool, for bindings that allocate a fresh output per
+// primitive (every Eval rule of the reference does, candle.rs:197-1004): no device synchronisation on either
+// side, freed blocks are reused by later allocations on the same stream.
+extern "C" int32_t rb_malloc_async(rb_ctx* ctx, size_t bytes, void** out) {
+  RB_REQUIRE(ctx && out, "rb_malloc_async: null argument");
+  *out = nullptr;
+  if (bytes == 0) return RB_OK;
+  if (!ctx->pool_ready) {
+    cudaMemPool_t pool = nullptr;
+    RB_CUDA(cudaDeviceGetDefaultMemPool(&pool, ctx->device));
+    unsigned long long keep = ~0ull;  // keep freed memory in the pool instead of returning it to the driver
+    RB_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+    ctx->pool_ready = true;
+  }
+  cudaError_t e = cudaMallocAsync(out, bytes, ctx->stream);
+  if (e == cudaErrorMemoryAllocation) {
+    cudaGetLastError();
+    return fail(RB_ERR_OOM, "rb_malloc_async: out of device memory asking for %zu bytes", bytes);
+  }
+  RB_CUDA(e);
+  return RB_OK;
+}
+
+extern "C" int32_t rb_free_async(rb_ctx* ctx, void* dev) {
+  RB_REQUIRE(ctx, "rb_free_async: null context");
+  if (!dev) return RB_OK;
+  // ordered after everything already issued on the context's stream; tensor maps keyed by this address stay
+  // valid for a later allocation of the same address and shape, and are dropped wholesale when the table fills
+  RB_CUDA(cudaFreeAsync(dev, ctx->stream));
+  return RB_OK;
+}
+
 extern "C" int32_t rb_free(rb_ctx* ctx, void* dev) {
   RB_REQUIRE(ctx, "rb_free: null context");
   if (!dev) return RB_OK;

@@ -23,6 +23,7 @@ struct rb_ctx {
   unsigned long long* argmax_best = nullptr;
   unsigned int* argmax_count = nullptr;
   // split-KV partials of the decode attention: grown on demand, owned by the context (one stream at a time)
+  bool pool_ready = false;  // the device's default memory pool has been told to keep freed blocks
   float* attn_scratch = nullptr;
   size_t attn_scratch_bytes = 0;
   bool debug_simple = false;

@@ -132,3 +132,33 @@ def test_rope_tables_match_oracle(cuda):
         s_ref, c_ref = rai_cpu.rope_tables(dim, n, theta, name)
         assert float((cos.cpu() - c_ref[:, : dim // 2]).abs().max()) < 2e-5
         assert float((sin.cpu() - s_ref[:, : dim // 2]).abs().max()) < 2e-5
+
+
+def test_pooled_stream_ordered_allocation(cuda):
+    """rb_malloc_async / rb_free_async: no synchronisation, blocks reused in stream order, contents intact."""
+    import ctypes
+    import time
+    import numpy as np
+    from rai_b200 import _lib
+    n = 1 << 20
+    host = np.arange(n, dtype=np.float32)
+    back = np.empty_like(host)
+    seen = set()
+    t0 = time.perf_counter()
+    for i in range(200):
+        p = ctypes.c_void_p()
+        _lib.call("rb_malloc_async", cuda.ctx, n * 4, ctypes.byref(p))
+        assert p.value and p.value % 256 == 0
+        seen.add(p.value)
+        if i % 50 == 0:
+            _lib.call("rb_upload", cuda.ctx, p, host.ctypes.data_as(ctypes.c_void_p), n * 4)
+            _lib.call("rb_download", cuda.ctx, back.ctypes.data_as(ctypes.c_void_p), p, n * 4)
+            assert np.array_equal(back, host)
+        _lib.call("rb_free_async", cuda.ctx, p)
+    cuda.synchronize()
+    assert len(seen) <= 4, "freed blocks should be reused by the next allocation on the stream"
+    assert time.perf_counter() - t0 < 2.0
+    empty = ctypes.c_void_p(1)
+    _lib.call("rb_malloc_async", cuda.ctx, 0, ctypes.byref(empty))
+    assert not empty.value
+    _lib.call("rb_free_async", cuda.ctx, None)
