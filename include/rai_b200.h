@@ -194,7 +194,7 @@ int32_t rb_attention_decode_static(rb_ctx* ctx, const void* q_dev, rb_kv_cache* 
 
 /* rb_rope_kv_append followed by rb_attention for a single new token per sequence (s_new == 1), the step a
  * KV-cached decode repeats (qwen2.rs:176-216 with seq_len 1): same inputs, same results bit for bit.  For bf16
- * caches with head_dim 64, 128 or 256 and a rotary width that is a multiple of 16 both run as ONE kernel: the
+ * caches with head_dim 64, 80, 96, 128 or 256 and a rotary width that is a multiple of 16 both run as ONE kernel: the
  * attention kernel rotates q and k itself, appends k/v to the cache, and can start fetching old K/V pages
  * before the projection that feeds it has finished; q_scratch_dev ([batch, q_heads, head_dim]) is then not
  * touched.  Every other case runs the two calls one after the other, through q_scratch_dev. */

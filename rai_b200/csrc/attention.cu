@@ -136,7 +136,7 @@ attention_kernel(const AParams p, const __grid_constant__ CUtensorMap tm_k, cons
   // sequence lengths are set by a kernel that does not release its dependents early (so it completed before
   // anything after it started), and K/V rows of earlier tokens were written by earlier steps.  The one
   // row that is not there yet, the new token's, is patched into the staged tile from registers below.
-  const bool fuse = DECODE && TMA && p.fuse != 0;
+  const bool fuse = DECODE && p.fuse != 0;
   if (!fuse) pdl_wait();  // q and the newest K/V rows come from the kernel before this one
 
   int b, head, kvh, q0 = 0, split = 0;
@@ -209,14 +209,16 @@ attention_kernel(const AParams p, const __grid_constant__ CUtensorMap tm_k, cons
   // the new token's tile and slot, and whether this block is the one that walks it (fused step)
   const int new_tile = (len - 1) / kTile, new_slot = (len - 1) % kTile;
   const bool owns_new = fuse && new_tile >= tile_lo && new_tile < tile_hi;
-  __shared__ __align__(16) bf16 new_kv[(DECODE && TMA) ? 2 * D : 8];  // the new token's k row, then its v row
+  __shared__ __align__(16) bf16 new_kv[DECODE ? 2 * D : 8];  // the new token's k row, then its v row
 
   if (fuse) {
-    if constexpr (DECODE && TMA) {
-      // first tiles on their way before the projection's output exists
+    if constexpr (DECODE) {
+      // first tiles on their way before the projection's output exists (one commit group each, like the other path)
 #pragma unroll
-      for (int s = 0; s < C::kStages - 1; ++s)
+      for (int s = 0; s < C::kStages - 1; ++s) {
         if (tile_lo + s < tile_hi) load_tile(tile_lo + s, s);
+        cp_async_commit();
+      }
       pdl_wait();
       // q heads of this KV head, its k head and its v head out of the projection's row of this sequence
       const int ncol = (p.q_heads + 2 * p.kv_heads) * D;
@@ -330,18 +332,18 @@ attention_kernel(const AParams p, const __grid_constant__ CUtensorMap tm_k, cons
       if (it == 0) cp_async_wait<0>();  // Q
       const bool mine = ptx::mbar_wait(&full_bar[it % C::kStages], (uint32_t)(it / C::kStages) & 1u, &abort_flag);
       if (!__syncthreads_and(mine)) { aborted = true; break; }  // uniform decision: nobody computes on a tile that never came
-      if (owns_new && tile == new_tile) {
-        // the copy of this tile may predate the new token's row: put the row in place from the block's own copy
-        uint8_t* ks_w = kv_s + (it % C::kStages) * C::kStageBytes;
-        for (int i = threadIdx.x; i < 2 * (D / 8); i += blockDim.x) {
-          const int is_v = i / (D / 8), c = i % (D / 8);
-          *reinterpret_cast<uint4*>(ks_w + is_v * C::kTileBytes + tile_off(new_slot, c * 8)) =
-              *reinterpret_cast<const uint4*>(new_kv + is_v * D + c * 8);
-        }
-        __syncthreads();
-      }
     } else {
       cp_async_wait<C::kStages - 1>();
+      __syncthreads();
+    }
+    if (owns_new && tile == new_tile) {
+      // the copy of this tile may predate the new token's row: put the row in place from the block's own copy
+      uint8_t* ks_w = kv_s + (it % C::kStages) * C::kStageBytes;
+      for (int i = threadIdx.x; i < 2 * (D / 8); i += blockDim.x) {
+        const int is_v = i / (D / 8), c = i % (D / 8);
+        *reinterpret_cast<uint4*>(ks_w + is_v * C::kTileBytes + tile_off(new_slot, c * 8)) =
+            *reinterpret_cast<const uint4*>(new_kv + is_v * D + c * 8);
+      }
       __syncthreads();
     }
     if (C::kQInRegs && !q_loaded) {
@@ -701,7 +703,7 @@ bool attention_can_fuse_rope(const rb_kv_cache* c, int q_heads, int rot, const v
                              const void* bias, const float* cos_t, const float* sin_t, int batch) {
   auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   const int d = c->head_dim;
-  if (c->dtype != RB_BF16 || (d % 64) != 0 || d > 256) return false;
+  if (c->dtype != RB_BF16 || !(d == 64 || d == 80 || d == 96 || d == 128 || d == 256)) return false;
   if (rot < 0 || rot > d || (rot % 16) != 0 || ((d - rot) % 8) != 0) return false;
   if (q_heads % c->kv_heads != 0 || q_heads / c->kv_heads > 16) return false;
   const size_t acc_stride = (size_t)batch * (q_heads + 2 * c->kv_heads) * d;
@@ -743,10 +745,12 @@ int attention_decode_fused_rope(rb_ctx* ctx, const void* qkv, const float* acc, 
   for (int b = 0; b < batch; ++b) max_len = std::max(max_len, c->host_lens[b]);
   switch (c->head_dim) {
     case 64: return launch_attention<64>(ctx, c, p, batch, max_len);
+    case 80: return launch_attention<80>(ctx, c, p, batch, max_len);
+    case 96: return launch_attention<96>(ctx, c, p, batch, max_len);
     case 128: return launch_attention<128>(ctx, c, p, batch, max_len);
     case 256: return launch_attention<256>(ctx, c, p, batch, max_len);
   }
-  return fail(RB_ERR_UNIMPLEMENTED, "fused rope + attention: head_dim %d unsupported (64, 128, 256)", c->head_dim);
+  return fail(RB_ERR_UNIMPLEMENTED, "fused rope + attention: head_dim %d unsupported (64, 80, 96, 128, 256)", c->head_dim);
 }
 
 }  // namespace rb

@@ -25,6 +25,10 @@ CASES = [  # (nq, nkv, d, rot, batch, tokens already cached, form)
     (14, 2, 64, 64, 2, 1500, "partials"),  # several KV splits: only the last one appends
     (1, 1, 64, 64, 2, 1000, "rows"),       # one head per KV head, split
     (4, 4, 128, 64, 1, 1023, "partials+bias"),
+    (2, 2, 80, 32, 2, 33, "rows"),            # phi2: head_dim 80, partial rotary, padded-row loads
+    (4, 4, 80, 32, 3, 200, "partials+bias"),
+    (2, 2, 96, 96, 1, 129, "partials"),       # phi3 head size
+    (8, 8, 96, 96, 2, 700, "rows+partials"),  # several KV splits on the padded-row path
 ]
 
 
