@@ -400,8 +400,10 @@ def run_ours(args):
     dev.synchronize()
 
     # ---- the same steps as the device ran them (graph replay, overlap included): a tracing pass of its own
+    # (single GPU only: the decode steps of a tensor-parallel group are collective, so a pass that one rank runs
+    # alone would leave it waiting for peers that never come)
     in_graph = None
-    if rank == 0 and not args.skip_timeline:
+    if world == 1 and not args.skip_timeline:
         try:
             in_graph = decode_timeline(model, dev, rewind, first, T0, args.timeline or None)
         except Exception as e:  # tracing is an extra: the bench line does not depend on it
