@@ -32,3 +32,14 @@ def test_other_ranks_of_the_reference_arm_exit_quietly():
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2", "--config",
                         "tiny-qwen2", "--steps", "1", "--warmup", "0"], capture_output=True, text=True, timeout=300, cwd=ROOT, env=env)
     assert r.returncode == 0 and r.stdout.strip() == ""
+
+
+def test_single_rank_passes_of_the_gpu_arm_are_not_collective():
+    """A tensor-parallel decode step is collective (exchange flags, NCCL gathers): any extra pass over decode steps must
+    run on every rank or on single-GPU runs only.  The device-timeline pass is the one extra that is rank-local."""
+    import re
+    src = open(os.path.join(ROOT, "bench.py")).read()
+    calls = [m.start() for m in re.finditer(r"in_graph = decode_timeline\(", src)]
+    assert len(calls) == 1
+    guard = src.rfind("if ", 0, calls[0])
+    assert "world == 1" in src[guard:calls[0]], "the timeline pass must be limited to single-GPU runs"
