@@ -273,6 +273,10 @@ def workload_config(args, cfg, n):
 # --------------------------------------------------------------------------------------------------
 def run_ours(args):
     import torch
+    if args.shard_of > 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        # developer aid: needs the developer build of the library (python -m rai_b200.build --debug-aids)
+        os.environ["RAI_B200_DEBUG_AIDS"] = "1"
+        os.environ["RAI_B200_SHARD_ONLY"] = "1"
     from rai_b200 import _lib, configs, synth
     from rai_b200.device import Cuda
     from rai_b200.models import Model
@@ -311,8 +315,6 @@ def run_ours(args):
     cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], max_seq)
     max_tokens = max(B * chunk, 0 if args.skip_prefill else PB * PS)
     dev = Cuda(local)
-    if args.shard_of > 1 and world == 1:
-        os.environ["RAI_B200_SHARD_ONLY"] = "1"
     model = Model(cfg, _lib.BF16, dev, max(B, PB), max_seq, max_tokens, tp_rank=rank,
                   tp_size=args.shard_of if (args.shard_of > 1 and world == 1) else world)
     if world > 1:

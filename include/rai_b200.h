@@ -87,6 +87,18 @@ const char* rb_last_error(void);
 /* Copies the 4-word device status record {code, where, detail0, detail1} to `out4` (synchronises). */
 int32_t rb_status_word(rb_ctx* ctx, uint32_t* out4);
 int32_t rb_sm_count(rb_ctx* ctx);
+/* How long a device-side wait (on a copy, a tensor-core result or a tensor-parallel peer) may last before the
+ * kernel gives up, reports RB_ERR_TIMEOUT through the status word and returns.  Default: about one second.
+ * Stands in for nothing in the reference, whose only device code is candle's; it is the knob behind the
+ * "never blocks without bound" convention above.  Applies to launches made after the call. */
+int32_t rb_set_wait_budget_us(rb_ctx* ctx, int64_t microseconds);
+/* Self-test of the give-up path, for test suites: runs a kernel whose wait can never be satisfied (`which` 0: an
+ * mbarrier nothing arrives on, waited for with the library's own helper; 1: the tensor-parallel norm of a
+ * two-member group whose second member, zeroed memory of this GPU, never raises its flag), with the given
+ * budget.  The kernel returns when the budget runs out; RB_OK means the give-up was recorded as designed
+ * (RB_ERR_TIMEOUT with the kernel's tag, outputs untouched), and the status word is clear again on return.
+ * Nothing faults, traps or spins without bound.  No counterpart in the reference. */
+int32_t rb_selftest_wait_gives_up(rb_ctx* ctx, int32_t which, int64_t budget_us);
 
 /* Device memory owned by the library (`TensorLike` storage, rai-core/src/tensor.rs:19-26). */
 int32_t rb_malloc(rb_ctx* ctx, size_t bytes, void** out_dev);
@@ -148,6 +160,10 @@ int32_t rb_kv_cache_create(rb_ctx* ctx, int32_t layers, int32_t kv_heads, int32_
 int32_t rb_kv_cache_destroy(rb_kv_cache* c);
 /* clear_kv_cache, rai-models/src/llm/qwen2.rs:361-365: every sequence length back to 0. */
 int32_t rb_kv_cache_reset(rb_kv_cache* c);
+/* The sliding-window term of qwen2's mask (rai-models/src/llm/qwen2.rs:316-334): attention over this cache hides
+ * key j from query i when both belong to the tokens of the same call and j + window < i (the reference's mask
+ * leaves the cached prefix visible, and builds no mask for a single-token call).  Default: no window. */
+int32_t rb_kv_cache_set_window(rb_kv_cache* c, int32_t window);
 /* Host-side bookkeeping of Model::fwd's seqlen_offset: sequences 0..batch-1 now hold pos+s_new tokens. */
 int32_t rb_kv_cache_set_len(rb_kv_cache* c, int32_t batch, int32_t len);
 /* Test hook: copies K and V of tokens [t0, t0+n) of (layer, seq, kv_head) to host as [n, head_dim]. */
@@ -181,11 +197,14 @@ int32_t rb_attention(rb_ctx* ctx, const void* q_dev, rb_kv_cache* cache, int32_t
  * scratch with cudaMalloc when a larger shape arrives, which is off limits to a host runtime that owns
  * all device memory through its own pool, and unwelcome in a serving loop because an allocation can
  * synchronise the whole device.  This variant keeps that scratch in a 4 MiB array built into the
- * library (held by every GPU that loads it, until exit) and calls no allocator of any kind.
+ * library (held by every GPU that loads it, until exit) and calls neither cudaMalloc nor cudaFree nor any
+ * allocating library routine.  (The CUDA runtime itself may still load a kernel's code the first time that
+ * kernel is launched: make the first call per head size before the host's pool takes the remaining memory.)
  *   - limit: batch * q_heads * splits * (head_dim + 2) floats must fit in 1 Mi floats; larger shapes are
  *     rejected with RB_ERR_INVALID and a message naming the sizes (use rb_attention for those);
  *   - the first call on a device looks up the array's device address (one cudaGetSymbolAddress, the
- *     context's device must be current); make that first call before any stream capture;
+ *     context's device must be current; the look-up is guarded by a lock, so first calls from several threads are
+ *     safe); make that first call before any stream capture;
  *   - all calls share the one array: two calls whose kernels overlap on the GPU (different streams or
  *     contexts of one process) race on it; calls on one stream are safe.  Nothing in it needs to start at
  *     zero: every slot a call reads was written by that call. */
@@ -278,6 +297,11 @@ typedef struct rb_model_config {
   int32_t max_tokens;              /* largest batch*seq of one forward call (workspace size) */
   int32_t tp_rank;                 /* tensor-parallel rank / size (1 = single GPU) */
   int32_t tp_size;
+  int32_t sliding_window;          /* Config::sliding_window (qwen2.rs:24,316-334): among the tokens of one forward call,
+                                      key j is masked for query i when j + sliding_window < i; cached tokens stay
+                                      visible and a single-token call has no mask, exactly as the reference builds it.
+                                      Honoured for RB_ARCH_QWEN2 (the one family whose mask has the term); 0 = none */
+  int32_t reserved0;               /* keeps the doubles 8-byte aligned; set to 0 */
   double rope_theta;
   double norm_eps;
 } rb_model_config;

@@ -14,7 +14,8 @@ from typing import Dict, List, Tuple
 
 PKG = Path(__file__).resolve().parent
 HEADER = PKG.parent / "include" / "rai_b200.h"
-LIB_PATH = PKG / "librai_b200.so"
+# RAI_B200_DEBUG_AIDS=1 selects the developer build (python -m rai_b200.build --debug-aids), a file of its own
+LIB_PATH = PKG / ("librai_b200_dbg.so" if __import__("os").environ.get("RAI_B200_DEBUG_AIDS") == "1" else "librai_b200.so")
 
 # status codes / tags of the header, mirrored for Python callers
 RB_OK = 0
@@ -42,7 +43,7 @@ class ModelConfig(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in (
         "arch", "dtype", "vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers",
         "num_attention_heads", "num_key_value_heads", "max_position_embeddings", "rotary_dim", "hidden_act",
-        "tie_word_embeddings", "max_batch", "max_seq", "max_tokens", "tp_rank", "tp_size")] + [
+        "tie_word_embeddings", "max_batch", "max_seq", "max_tokens", "tp_rank", "tp_size", "sliding_window", "reserved0")] + [
         ("rope_theta", ctypes.c_double), ("norm_eps", ctypes.c_double)]
 
 

@@ -1,7 +1,10 @@
 """Builds librai_b200.so in-tree with nvcc for sm_100a (no GPU needed: nvcc cross-compiles).
 
-    python -m rai_b200.build            # incremental
-    python -m rai_b200.build --force    # rebuild everything
+    python -m rai_b200.build               # incremental
+    python -m rai_b200.build --force       # rebuild everything
+    python -m rai_b200.build --debug-aids  # a second library, librai_b200_dbg.so, compiled with -DRB_DEBUG_AIDS
+                                           # (developer switches such as running one tensor-parallel shard alone);
+                                           # loaded instead of the product library when RAI_B200_DEBUG_AIDS=1
 """
 from __future__ import annotations
 
@@ -17,7 +20,7 @@ OBJ = PKG / "csrc" / "build"
 LIB = PKG / "librai_b200.so"
 HEADER = PKG.parent / "include" / "rai_b200.h"
 
-SOURCES = ["api.cu", "decoder_kernels.cu", "plain_kernels.cu", "primitives.cu", "gemm_tc.cu", "attention.cu", "model.cu", "safetensors.cu"]
+SOURCES = ["api.cu", "decoder_kernels.cu", "plain_kernels.cu", "primitives.cu", "gemm_tc.cu", "attention.cu", "model.cu", "safetensors.cu", "selftest.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -39,7 +42,13 @@ def _stale(target: Path, deps) -> bool:
     return any(Path(d).stat().st_mtime > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+def build(force: bool = False, verbose: bool = False, debug_aids: bool = False) -> Path:
+    global OBJ, LIB
+    flags = list(NVCC_FLAGS)
+    if debug_aids:
+        OBJ, LIB, flags = CSRC / "build_dbg", PKG / "librai_b200_dbg.so", flags + ["-DRB_DEBUG_AIDS"]
+    else:
+        OBJ, LIB = CSRC / "build", PKG / "librai_b200.so"
     OBJ.mkdir(parents=True, exist_ok=True)
     headers = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + [HEADER]
     nvcc = _nvcc()
@@ -47,7 +56,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     for src in SOURCES:
         s, o = CSRC / src, OBJ / (src + ".o")
         if force or _stale(o, [s] + headers):
-            cmd = [nvcc, *NVCC_FLAGS, "-c", str(s), "-o", str(o)]
+            cmd = [nvcc, *flags, "-c", str(s), "-o", str(o)]
             if verbose:
                 cmd.insert(1, "-Xptxas")
                 cmd.insert(2, "-v")
@@ -75,5 +84,5 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
 
 if __name__ == "__main__":
-    p = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    p = build(force="--force" in sys.argv, verbose="-v" in sys.argv, debug_aids="--debug-aids" in sys.argv)
     print(p)

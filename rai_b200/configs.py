@@ -116,6 +116,9 @@ def to_struct(cfg: dict, dtype: int, max_batch: int, max_seq: int, max_tokens: i
     s.tie_word_embeddings = int(tied(cfg))
     s.max_batch, s.max_seq, s.max_tokens = int(max_batch), int(max_seq), int(max_tokens)
     s.tp_rank, s.tp_size = int(tp_rank), int(tp_size)
+    # only qwen2's mask has the sliding-window term (qwen2.rs:316-327); the other families' masks are plain causal
+    s.sliding_window = int(cfg.get("sliding_window") or 0) if cfg["arch"] == "qwen2" else 0
+    s.reserved0 = 0
     s.rope_theta = float(cfg["rope_theta"])
     s.norm_eps = float(norm_eps(cfg))
     return s

@@ -58,6 +58,11 @@ extern "C" int32_t rb_init(int32_t device, rb_ctx** out) {
   rb_ctx* c = new rb_ctx();
   c->device = device;
   c->sm_count = prop.multiProcessorCount;
+  {
+    int khz = 0;
+    if (cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, device) == cudaSuccess && khz > 0) c->cycles_per_us = khz / 1000.0;
+    else cudaGetLastError();
+  }
   RB_CUDA(cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking));
   c->stream = c->own_stream;
   RB_CUDA(cudaMalloc(&c->status_dev, 4 * sizeof(uint32_t)));
@@ -66,6 +71,8 @@ extern "C" int32_t rb_init(int32_t device, rb_ctx** out) {
   RB_CUDA(cudaMalloc(&c->argmax_count, kArgmaxRows * sizeof(unsigned int)));
   RB_CUDA(cudaMemset(c->argmax_best, 0, kArgmaxRows * sizeof(unsigned long long)));
   RB_CUDA(cudaMemset(c->argmax_count, 0, kArgmaxRows * sizeof(unsigned int)));
+  RB_CUDA(cudaMalloc(&c->gemm_tile_count, 2 * kGemmMaxReduceTiles * sizeof(uint32_t)));
+  RB_CUDA(cudaMemset(c->gemm_tile_count, 0, 2 * kGemmMaxReduceTiles * sizeof(uint32_t)));
   const char* dbg = getenv("RAI_B200_SIMPLE");
   c->debug_simple = dbg && dbg[0] == '1';
   const char* dg = getenv("RAI_B200_SIMPLE_GEMM");
@@ -76,6 +83,11 @@ extern "C" int32_t rb_init(int32_t device, rb_ctx** out) {
   c->debug_no_fuse = nf && nf[0] == '0';
   const char* pdl = getenv("RAI_B200_PDL");
   c->pdl = !(pdl && pdl[0] == '0');
+  if (const char* gr = getenv("RAI_B200_GEMM_REDUCE")) c->gemm_reduce = gr[0] != '0';
+  if (const char* rk = getenv("RAI_B200_GEMM_RING_KB")) {
+    const long kb = atol(rk);
+    if (kb >= 32 && kb <= 200) c->gemm_ring_bytes = (size_t)kb * 1024;
+  }
   *out = c;
   return RB_OK;
 }
@@ -89,6 +101,9 @@ extern "C" int32_t rb_destroy(rb_ctx* ctx) {
   if (ctx->argmax_best) cudaFree(ctx->argmax_best);
   if (ctx->argmax_count) cudaFree(ctx->argmax_count);
   if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);
+  for (void* r : ctx->retired) cudaFree(r);
+  if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
+  if (ctx->gemm_tile_count) cudaFree(ctx->gemm_tile_count);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
   delete ctx;
   return RB_OK;
@@ -114,8 +129,24 @@ extern "C" int32_t rb_sync(rb_ctx* ctx) {
   if (w[0] != 0) {
     RB_CUDA(cudaMemset(ctx->status_dev, 0, 4 * sizeof(uint32_t)));
     const int code = -(int)w[0];
+    if (code == RB_ERR_TIMEOUT) {
+      // blocks that gave up returned before they were counted: re-arm the self-resetting arrival counters
+      for (rb_kv_cache* kc : ctx->caches)
+        RB_CUDA(cudaMemset(kc->split_count, 0, (size_t)kc->max_batch * kc->kv_heads * sizeof(uint32_t)));
+      RB_CUDA(cudaMemset(ctx->argmax_best, 0, kArgmaxRows * sizeof(unsigned long long)));
+      RB_CUDA(cudaMemset(ctx->argmax_count, 0, kArgmaxRows * sizeof(unsigned int)));
+      RB_CUDA(cudaMemset(ctx->gemm_tile_count, 0, 2 * kGemmMaxReduceTiles * sizeof(uint32_t)));
+    }
     return fail(code, "device-side check failed: code %d at 0x%x (detail %u, %u)", code, w[1], w[2], w[3]);
   }
+  return RB_OK;
+}
+
+extern "C" int32_t rb_set_wait_budget_us(rb_ctx* ctx, int64_t microseconds) {
+  RB_REQUIRE(ctx, "rb_set_wait_budget_us: null context");
+  RB_REQUIRE(microseconds >= 1 && microseconds <= 60000000, "rb_set_wait_budget_us: %lld us outside [1, 60 000 000]",
+             (long long)microseconds);
+  ctx->wait_budget_cycles = (long long)((double)microseconds * ctx->cycles_per_us);
   return RB_OK;
 }
 
@@ -246,6 +277,7 @@ extern "C" int32_t rb_kv_cache_create(rb_ctx* ctx, int32_t layers, int32_t kv_he
   RB_CUDA(cudaMemsetAsync(c->split_count, 0, (size_t)max_batch * kv_heads * sizeof(uint32_t), ctx->stream));
   RB_CUDA(cudaStreamSynchronize(ctx->stream));
   c->host_lens.assign(max_batch, 0);
+  ctx->caches.push_back(c);
   *out = c;
   return RB_OK;
 }
@@ -253,6 +285,8 @@ extern "C" int32_t rb_kv_cache_create(rb_ctx* ctx, int32_t layers, int32_t kv_he
 extern "C" int32_t rb_kv_cache_destroy(rb_kv_cache* c) {
   if (!c) return RB_OK;
   cudaStreamSynchronize(c->ctx->stream);
+  for (auto it = c->ctx->caches.begin(); it != c->ctx->caches.end(); ++it)
+    if (*it == c) { c->ctx->caches.erase(it); break; }
   if (c->k) cudaFree(c->k);
   if (c->v) cudaFree(c->v);
   if (c->block_table) cudaFree(c->block_table);
@@ -266,6 +300,13 @@ extern "C" int32_t rb_kv_cache_reset(rb_kv_cache* c) {
   RB_REQUIRE(c, "rb_kv_cache_reset: null cache");
   RB_CUDA(cudaMemsetAsync(c->seq_lens, 0, (size_t)c->max_batch * sizeof(int32_t), c->ctx->stream));
   c->host_lens.assign(c->max_batch, 0);
+  return RB_OK;
+}
+
+extern "C" int32_t rb_kv_cache_set_window(rb_kv_cache* c, int32_t window) {
+  RB_REQUIRE(c, "rb_kv_cache_set_window: null cache");
+  RB_REQUIRE(window >= 0, "rb_kv_cache_set_window: negative window %d", window);
+  c->window = window > (1 << 30) ? (1 << 30) : window;   // key + window must not overflow an int
   return RB_OK;
 }
 
@@ -307,6 +348,7 @@ extern "C" int32_t rb_linear(rb_ctx* ctx, const void* x, const void* w, const vo
   GemmArgs a;
   a.x = x; a.w = w; a.bias = bias; a.residual = residual; a.out = out;
   a.m = m; a.n = n; a.k = k; a.act = act;
+  a.reduce = ctx->gemm_reduce;  // decode-sized with few weight tiles: split K over idle SMs, summed inside the kernel
   const double es = (double)dtype_size(dtype);
   ProfScope prof(ctx, RB_PROF_GEMM, es * ((double)n * k + (double)m * k + (double)m * n * (residual ? 2 : 1) + (bias ? n : 0)),
                  2.0 * m * n * k);
@@ -321,6 +363,7 @@ extern "C" int32_t rb_gated_linear(rb_ctx* ctx, const void* x, const void* wg, c
   GemmArgs a;
   a.x = x; a.w = wg; a.w2 = wu; a.out = out;
   a.m = m; a.n = n; a.k = k; a.act = act;
+  a.reduce = ctx->gemm_reduce;
   const double es = (double)dtype_size(dtype);
   ProfScope prof(ctx, RB_PROF_GEMM, es * (2.0 * n * k + (double)m * k + (double)m * n), 4.0 * m * n * k);
   if (dtype == RB_BF16 && !ctx->debug_simple_gemm) return gemm_tc_bf16(ctx, a);

@@ -26,6 +26,20 @@ using bf16 = __nv_bfloat16;
 
 int attention_decode_splits(rb_ctx* ctx, int batch, int kv_heads, int max_len);
 
+// Split-KV scratch of the context, grow-only.  A captured decode step has the buffer's address baked in, and other
+// models or direct calls on the same context may need more later: a buffer that has been handed out is therefore
+// never freed before rb_destroy - growing allocates a new one and retires the old one.  Models reserve their
+// worst case when they are created, so a generation does not allocate.
+int attention_reserve_scratch(rb_ctx* ctx, size_t bytes) {
+  if (ctx->attn_scratch_bytes >= bytes) return RB_OK;
+  float* fresh = nullptr;
+  RB_CUDA(cudaMalloc(&fresh, bytes));
+  if (ctx->attn_scratch) ctx->retired.push_back(ctx->attn_scratch);
+  ctx->attn_scratch = fresh;
+  ctx->attn_scratch_bytes = bytes;
+  return RB_OK;
+}
+
 namespace {
 
 constexpr int kTile = 64;  // keys per tile == tokens per cache page
@@ -86,6 +100,8 @@ struct AParams {
   const int32_t* seq_lens;
   int pages_per_seq, s_new, q_heads, kv_heads, group;
   int n_splits;
+  int window;      // sliding window (qwen2.rs:316-327): among the tokens of one call, key j is hidden from row i when j + window < i
+  long long wait_cycles;  // give-up budget of the bounded waits
   float scale_log2;
   bf16* out;
   float* part_o;   // [batch*q_heads][n_splits][D]
@@ -158,7 +174,10 @@ attention_kernel(const AParams p, const __grid_constant__ CUtensorMap tm_k, cons
     tile_lo = split * per;
     tile_hi = min(total, tile_lo + per);
   } else {
-    tile_lo = 0;
+    // The reference's window term acts among the tokens of ONE call only (qwen2.rs:316-334: the mask block of the
+    // cached prefix is all zeros, and a single-token call builds no mask at all, qwen2.rs:340-342), so whole tiles
+    // can be skipped only when nothing is cached.
+    tile_lo = base == 0 ? max(0, q0 - p.window) / kTile : 0;
     tile_hi = (min(base + q0 + 64, len) + kTile - 1) / kTile;
   }
   if (fuse && (len < 1 || len > p.f_max_seq)) {  // the same guard the separate RoPE/append kernel has
@@ -330,7 +349,7 @@ attention_kernel(const AParams p, const __grid_constant__ CUtensorMap tm_k, cons
     }
     if (TMA) {
       if (it == 0) cp_async_wait<0>();  // Q
-      const bool mine = ptx::mbar_wait(&full_bar[it % C::kStages], (uint32_t)(it / C::kStages) & 1u, &abort_flag);
+      const bool mine = ptx::mbar_wait(&full_bar[it % C::kStages], (uint32_t)(it / C::kStages) & 1u, &abort_flag, p.wait_cycles);
       if (!__syncthreads_and(mine)) { aborted = true; break; }  // uniform decision: nobody computes on a tile that never came
     } else {
       cp_async_wait<C::kStages - 1>();
@@ -385,7 +404,9 @@ attention_kernel(const AParams p, const __grid_constant__ CUtensorMap tm_k, cons
         for (int e = 0; e < 4; ++e) {
           const int key_abs = tile_start + kw0 + nt * 8 + 2 * t + (e & 1);
           const int hf = e >> 1;
-          const float v = (key_abs <= lim[hf]) ? s[nt][e] * p.scale_log2 : -INFINITY;
+          // causal limit (lim is the row's own position) and, among the new tokens only, the sliding window
+          const bool seen = key_abs <= lim[hf] && (DECODE || key_abs < base || key_abs + p.window >= lim[hf]);
+          const float v = seen ? s[nt][e] * p.scale_log2 : -INFINITY;
           s[nt][e] = v;
           mx[hf] = fmaxf(mx[hf], v);
         }
@@ -436,7 +457,7 @@ attention_kernel(const AParams p, const __grid_constant__ CUtensorMap tm_k, cons
       volatile uint32_t never = 0;
 #pragma unroll
       for (int s = 0; s < C::kStages; ++s)
-        if (armed_it[s] >= 0) ptx::mbar_wait(&full_bar[s], (uint32_t)(armed_it[s] / C::kStages) & 1u, &never);
+        if (armed_it[s] >= 0) ptx::mbar_wait(&full_bar[s], (uint32_t)(armed_it[s] / C::kStages) & 1u, &never, p.wait_cycles);
     }
     __syncthreads();
     return;
@@ -558,15 +579,14 @@ int launch_attn_kernel(rb_ctx* ctx, rb_kv_cache* c, const AParams& p, dim3 grid)
   static bool set[64] = {};  // the attribute belongs to the (kernel, device) pair
   const int dv = ctx->device & 63;
   if (!set[dv]) { RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes)); set[dv] = true; }
-  CUtensorMap none{};
-  const CUtensorMap *tk = &none, *tv = &none;
+  CUtensorMap tk{}, tv{};
   if (kTma) {
     // one map per layer and operand: rows are (page, KV head, token), 64-row x 64-column boxes
     const int64_t rows = (int64_t)c->num_pages * c->kv_heads * kTile;
     RB_TRY(tmap_2d_bf16(ctx, p.k, rows, D, D, kTile, &tk));
     RB_TRY(tmap_2d_bf16(ctx, p.v, rows, D, D, kTile, &tv));
   }
-  RB_CUDA(launch_kernel(kern, grid, dim3(128), (size_t)C::kSmemBytes, ctx->stream, ctx->pdl, p, *tk, *tv));
+  RB_CUDA(launch_kernel(kern, grid, dim3(128), (size_t)C::kSmemBytes, ctx->stream, ctx->pdl, p, tk, tv));
   ctx->launches++;
   return RB_OK;
 }
@@ -583,14 +603,7 @@ int launch_attention(rb_ctx* ctx, rb_kv_cache* c, AParams& p, int batch, int max
   const int splits = attention_decode_splits(ctx, batch, p.kv_heads, max_len);
   p.n_splits = splits;
   if (splits > 1) {
-    const size_t need = (size_t)batch * p.q_heads * splits * (D + 2) * sizeof(float);
-    if (ctx->attn_scratch_bytes < need) {
-      // cudaFree waits for the kernels that may still read the old buffer
-      if (ctx->attn_scratch) RB_CUDA(cudaFree(ctx->attn_scratch));
-      ctx->attn_scratch = nullptr; ctx->attn_scratch_bytes = 0;
-      RB_CUDA(cudaMalloc(&ctx->attn_scratch, need));
-      ctx->attn_scratch_bytes = need;
-    }
+    RB_TRY(attention_reserve_scratch(ctx, (size_t)batch * p.q_heads * splits * (D + 2) * sizeof(float)));
     p.part_o = ctx->attn_scratch;
     p.part_ml = ctx->attn_scratch + (size_t)batch * p.q_heads * splits * D;
   }
@@ -684,6 +697,8 @@ int attention_mma_bf16(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, in
   p.scale_log2 = scale * kLog2e;
   p.out = (bf16*)out;
   p.status = ctx->status_dev;
+  p.window = c->window;
+  p.wait_cycles = ctx->wait_budget_cycles;
   RB_REQUIRE(p.group >= 1 && p.group <= 16 && q_heads % c->kv_heads == 0,
              "attention: %d query heads per KV head unsupported (1..16)", p.group);
   int max_len = 0;
@@ -729,6 +744,8 @@ int attention_decode_fused_rope(rb_ctx* ctx, const void* qkv, const float* acc, 
   p.scale_log2 = scale * kLog2e;
   p.out = (bf16*)out;
   p.status = ctx->status_dev;
+  p.window = c->window;
+  p.wait_cycles = ctx->wait_budget_cycles;
   p.fuse = 1;
   p.f_qkv = (const bf16*)qkv;
   p.f_acc = n_acc > 0 ? acc : nullptr;
@@ -795,6 +812,8 @@ extern "C" int32_t rb_attention_decode_static(rb_ctx* ctx, const void* q, rb_kv_
   p.scale_log2 = scale * kLog2e;
   p.out = (bf16*)out;
   p.status = ctx->status_dev;
+  p.window = c->window;
+  p.wait_cycles = ctx->wait_budget_cycles;
   switch (c->head_dim) {
     case 64: return launch_attention_decode_static<64>(ctx, c, p, batch, max_len, scratch);
     case 80: return launch_attention_decode_static<80>(ctx, c, p, batch, max_len, scratch);

@@ -19,6 +19,14 @@ struct rb_ctx {
   // Tensor maps are keyed by (base pointer, rows, cols, row stride in elements, box rows).
   std::map<std::tuple<const void*, int64_t, int64_t, int64_t, int>, CUtensorMap> tmaps;
   bool pdl = true;            // RAI_B200_PDL=0 turns programmatic dependent launch off (debugging aid)
+  // shared memory a decode-sized GEMM spends on its operand ring (RAI_B200_GEMM_RING_KB overrides)
+  size_t gemm_ring_bytes = 200 * 1024;
+  bool gemm_reduce = true;    // RAI_B200_GEMM_REDUCE=0: tensor-parallel GEMMs leave split-K to separate kernels (debugging aid)
+  float* gemm_scratch = nullptr;   // float32 slabs of the GEMMs that reduce split-K inside the kernel; grow-only
+  size_t gemm_scratch_bytes = 0;
+  uint32_t* gemm_tile_count = nullptr;  // [2][kGemmMaxReduceTiles] arrival / done counters of those GEMMs, self-resetting
+  long long wait_budget_cycles = 2000000000LL;  // give-up time of every bounded device-side wait (rb_set_wait_budget_us)
+  int tmap_cache_limit = 4096;  // tensor maps kept before the cache is emptied
   // argmax across blocks: running best (key << 32 | index) and arrival count per row; self-resetting
   unsigned long long* argmax_best = nullptr;
   unsigned int* argmax_count = nullptr;
@@ -26,6 +34,9 @@ struct rb_ctx {
   bool pool_ready = false;  // the device's default memory pool has been told to keep freed blocks
   float* attn_scratch = nullptr;
   size_t attn_scratch_bytes = 0;
+  std::vector<void*> retired;  // outgrown scratch buffers, kept until rb_destroy (captured graphs may still name them)
+  std::vector<struct rb_kv_cache*> caches;  // live caches, for the clean-up after a device-side give-up
+  double cycles_per_us = 1965.0;  // SM clock, to turn a wait budget in microseconds into cycles
   bool debug_simple = false;
   bool debug_no_fuse = false;  // RAI_B200_FUSE_ROPE=0
   bool debug_simple_gemm = false, debug_simple_attn = false;  // RAI_B200_SIMPLE_GEMM / _ATTN: one kernel family only  // RAI_B200_SIMPLE=1: route bf16 through the plain kernels (debugging aid)
@@ -40,6 +51,7 @@ struct rb_kv_cache {
   rb_ctx* ctx = nullptr;
   int layers = 0, kv_heads = 0, head_dim = 0, max_batch = 0, max_seq = 0, dtype = RB_BF16;
   int pages_per_seq = 0, num_pages = 0;
+  int window = 1 << 30;  // sliding-window width of the attention mask (rb_kv_cache_set_window); 2^30 = none
   void* k = nullptr;
   void* v = nullptr;
   int32_t* block_table = nullptr;  // device [max_batch][pages_per_seq]
@@ -54,6 +66,7 @@ struct rb_kv_cache {
 // no round trip) and then raises a flag in every peer's flag array; the consumer waits (bounded) for
 // all flags and sums the copies in its own memory in rank order, the same on every rank.  Two slots,
 // chosen by the parity of a device-side sequence number, so replayed CUDA graphs need no new arguments.
+constexpr int kGemmMaxReduceTiles = 256;
 constexpr int kTpMaxRanks = 8;
 constexpr int kTpMaxRows = 256;
 struct TpPeers {
@@ -89,8 +102,7 @@ struct ProfScope {
 };
 
 // Internal launchers shared between api.cu and model.cu (defined next to their kernels).
-int tmap_2d_bf16(rb_ctx* ctx, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows,
-                 const CUtensorMap** out);
+int tmap_2d_bf16(rb_ctx* ctx, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, CUtensorMap* out);
 
 struct GemmArgs {
   const void* x = nullptr;      // [M, K]
@@ -103,9 +115,12 @@ struct GemmArgs {
   int act = RB_ACT_NONE;
   int n_split = 1;              // > 1: write float partials, no epilogue
   bool partials = false;
+  const TpPeers* push = nullptr;  // M <= 64: the result goes into this rank's place in every peer's exchange buffer
+  bool reduce = false;            // M <= 64: if K is split, sum the splits inside the kernel and apply the epilogue
 };
 int gemm_tc_bf16(rb_ctx* ctx, const GemmArgs& a);
 int gemm_tc_pick_splits(rb_ctx* ctx, int64_t m, int64_t n, int64_t k);
+int gemm_reserve_scratch(rb_ctx* ctx, size_t bytes);
 int gemm_simple(rb_ctx* ctx, const GemmArgs& a, int dtype);
 
 int attention_mma_bf16(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, int batch, int s_new, int q_heads,
@@ -126,6 +141,7 @@ int attention_decode_fused_rope(rb_ctx* ctx, const void* qkv, const float* acc, 
                                 const float* cos_t, const float* sin_t, int rot, rb_kv_cache* c, int layer, int batch,
                                 int q_heads, float scale, void* out);
 int attention_decode_splits(rb_ctx* ctx, int batch, int kv_heads, int max_len);
+int attention_reserve_scratch(rb_ctx* ctx, size_t bytes);
 int attention_simple(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, int batch, int s_new, int q_heads,
                      float scale, void* out, int dtype);
 }  // namespace rb

@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(512) norm_vec_kernel(int kind, const T* __rest
                                 const float* __restrict__ acc, int n_acc, size_t acc_stride,
                                 const T* __restrict__ acc_bias, const T* __restrict__ w, const T* __restrict__ b,
                                 float eps, int hidden, T* __restrict__ out, T* __restrict__ sum_out, const TpPeers tp,
-                                uint32_t* status) {
+                                uint32_t* status, long long wait_cycles) {
   __shared__ float red[32];
   __shared__ uint32_t tp_seq_s;
   pdl_launch_dependents();
@@ -161,7 +161,7 @@ __global__ void __launch_bounds__(512) norm_vec_kernel(int kind, const T* __rest
       bool ok = true;
       for (int r = 0; r < tp.size && ok; ++r) {
         while (ld_acquire_sys(mine + r) < seq) {
-          if (clock64() - t0 > 2000000000LL) { ok = false; break; }
+          if (clock64() - t0 > wait_cycles) { ok = false; break; }
         }
       }
       if (!ok) { status[0] = (uint32_t)(-RB_ERR_TIMEOUT); status[1] = 0x7A11u; status[2] = (uint32_t)tp.rank; status[3] = seq; }
@@ -641,7 +641,7 @@ static int norm_launch(rb_ctx* ctx, int kind, const void* x, const void* add, co
     auto go = [&](auto kern) {
       return launch_kernel(kern, dim3((unsigned)rows), dim3(threads), 0, ctx->stream, ctx->pdl, kind, (const T*)x,
                            (const T*)add, acc, n_acc, acc_stride, (const T*)acc_bias, (const T*)w, (const T*)b, eps,
-                           (int)hidden, (T*)out, (T*)sum_out, tp ? *tp : TpPeers{}, ctx->status_dev);
+                           (int)hidden, (T*)out, (T*)sum_out, tp ? *tp : TpPeers{}, ctx->status_dev, ctx->wait_budget_cycles);
     };
     if (tp) {
       if (chunks == 1) RB_CUDA(go(norm_vec_kernel<T, 1, true>));

@@ -16,8 +16,18 @@
 //   normal (SWAP = false): P = X, Q = W  — prefill-sized M.
 //   swapped (SWAP = true):  P = W, Q = X  — decode-sized M (<= 256): the weight matrix, which is
 //            all of the HBM traffic, streams through the 128-row side at full tile efficiency while
-//            the few activation rows ride along as the narrow N side.  Optional split-K over
-//            work items writes float32 partials that the consumer kernel sums in a fixed order.
+//            the few activation rows ride along as the narrow N side.  Two forms of split-K, both through
+//            float32 slabs in global memory (they stay in L2): `partials` leaves the slabs to the consumer
+//            kernel, which sums them in a fixed order while it reads its input anyway (the cheapest form on
+//            one GPU); `reduce` (M <= 64) sums them inside this kernel - every CTA holds one (tile, split),
+//            all are resident at once, the splits of a tile wait for one another (bounded) and each then
+//            sums one slice of the tile's rows in split order and applies the full epilogue (bias,
+//            activation, gating, residual) to it.  With `push` the finished slice goes into this rank's
+//            place in every tensor-parallel peer's exchange buffer (plain peer stores over NVLink) and the
+//            last CTA raises the flags: the row-parallel GEMM and its share of the allreduce are one kernel.
+//            (Running the splits of a tile as a thread-block cluster that reduces through distributed shared
+//            memory was built and measured: 5 us slower per launch, because a cluster is only scheduled once
+//            all its SMs are free and so loses the overlap with the previous kernel's tail.)
 // GATED computes act(X.Wg^T) * (X.Wu^T) with two accumulators per stage (qwen2.rs:100-103).
 //
 // Every barrier wait is bounded; a give-up is recorded in the context's status word and the CTA
@@ -72,16 +82,21 @@ struct Params {
   bf16* out;
   float* part;
   int act;
+  int stages;           // ring depth of this launch, 2..Cfg::kStages
+  int reduce;           // split-K reduced inside the kernel: the splits of a tile wait for one another (see the epilogue)
+  uint32_t* tile_count; // reduce: arrivals per tile, and readers done per tile; both self-resetting
+  uint32_t* tile_done;
+  int push;             // the output goes to the tensor-parallel peers' exchange buffers (see TpPeers)
+  long long wait_cycles;  // give-up budget of every bounded wait
   uint32_t* status;
-  unsigned long long* trace;  // debugging aid: 8 timestamps per CTA when non-null
+  TpPeers tp;
 };
 
-__device__ __forceinline__ unsigned long long gtime() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
 }
-#define RB_TRACE(slot) do { if (p.trace) p.trace[(size_t)blockIdx.x * 8 + (slot)] = gtime(); } while (0)
 
 __device__ __forceinline__ void decode_item(const Params& p, int item, bool swap, int& pt, int& qt, int& split) {
   if (swap) {
@@ -174,11 +189,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   __shared__ __align__(16) bf16 epi_tile[32 * kEpiPitch];  // 32 output rows x 128 columns, padded
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) RB_TRACE(0);
+  const int n_stages = p.stages;
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::kStages; ++s) { ptx::mbar_init(&full_bar[s], 1); ptx::mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < n_stages; ++s) { ptx::mbar_init(&full_bar[s], 1); ptx::mbar_init(&empty_bar[s], 1); }
     for (int a = 0; a < 2; ++a) { ptx::mbar_init(&acc_full[a], 1); ptx::mbar_init(&acc_empty[a], 4); }
     abort_flag = 0;
     issued_count = 0;
@@ -195,7 +210,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
-  if (threadIdx.x == 0) RB_TRACE(1);
 
   pdl_launch_dependents();
   if (warp == 0) {
@@ -224,18 +238,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
         else ptx::tma_load_2d(st, &tm_p, &full_bar[stage], kb * kBK, pt * kBM);
       };
       int n_pre = 0;
-      for (int item = blockIdx.x; item < p.n_items && n_pre < C::kStages; item += gridDim.x) {
+      for (int item = blockIdx.x; item < p.n_items && n_pre < n_stages; item += gridDim.x) {
         int pt, qt, split;
         decode_item(p, item, SWAP, pt, qt, split);
         const int kb0 = split * p.kb_per_split, kb1 = min(p.num_kb, kb0 + p.kb_per_split);
-        for (int kb = kb0; kb < kb1 && n_pre < C::kStages; ++kb, ++n_pre) {
+        for (int kb = kb0; kb < kb1 && n_pre < n_stages; ++kb, ++n_pre) {
           ptx::mbar_expect_tx(&full_bar[n_pre], C::kStageBytes);
           load_weights(tiles + (size_t)n_pre * C::kStageBytes, n_pre, kb, pt, qt);
         }
       }
-      RB_TRACE(2);
       pdl_wait();
-      RB_TRACE(3);
       int stage = 0;
       uint32_t phase = 0;
       uint32_t issued = 0;
@@ -247,17 +259,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
         for (int kb = kb0; kb < kb1; ++kb) {
           uint8_t* st = tiles + (size_t)stage * C::kStageBytes;
           if ((int)issued >= n_pre) {
-            if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_flag)) { ok = false; break; }
+            if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, &abort_flag, p.wait_cycles)) { ok = false; break; }
             ptx::mbar_expect_tx(&full_bar[stage], C::kStageBytes);
             load_weights(st, stage, kb, pt, qt);
           }
           load_activations(st, stage, kb, pt, qt);
           ++issued;
-          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+          if (++stage == n_stages) { stage = 0; phase ^= 1u; }
         }
       }
       issued_count = issued;
-      RB_TRACE(4);
       if (!ok) { p.status[0] = (uint32_t)(-RB_ERR_TIMEOUT); p.status[1] = 0x6E01u; p.status[2] = blockIdx.x; }
     }
   } else if (warp == 1) {
@@ -274,11 +285,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
         decode_item(p, item, SWAP, pt, qt, split);
         const int kb0 = split * p.kb_per_split, kb1 = min(p.num_kb, kb0 + p.kb_per_split);
         if (kb0 >= kb1) continue;  // empty split: the epilogue writes zeros on its own
-        if (!ptx::mbar_wait(&acc_empty[as], aphase ^ 1u, &abort_flag)) { ok = false; break; }
+        if (!ptx::mbar_wait(&acc_empty[as], aphase ^ 1u, &abort_flag, p.wait_cycles)) { ok = false; break; }
         ptx::tc_fence_after();
         const uint32_t d0 = tmem_base + (uint32_t)(as * C::kAccCols);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!ptx::mbar_wait(&full_bar[stage], phase, &abort_flag)) { ok = false; break; }
+          if (!ptx::mbar_wait(&full_bar[stage], phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
           ptx::tc_fence_after();
           const uint32_t st = ptx::smem_u32(tiles + (size_t)stage * C::kStageBytes);
           const uint32_t p0 = st, p1 = st + (C::kPTiles == 2 ? C::kPBytes : 0);
@@ -292,11 +303,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
                              acc);
           }
           ptx::umma_commit(&empty_bar[stage]);  // the stage is free once these MMAs have read it
-          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+          if (++stage == n_stages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
         ptx::umma_commit(&acc_full[as]);
-        RB_TRACE(5);
         if (++as == 2) { as = 0; aphase ^= 1u; }
       }
       if (!ok) { p.status[0] = (uint32_t)(-RB_ERR_TIMEOUT); p.status[1] = 0x6E02u; p.status[2] = blockIdx.x; }
@@ -319,14 +329,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
         continue;
       }
       // The four epilogue warps meet at named barriers below, so they must agree on giving up.
-      const bool mine = ptx::mbar_wait(&acc_full[as], aphase, &abort_flag);
+      const bool mine = ptx::mbar_wait(&acc_full[as], aphase, &abort_flag, p.wait_cycles);
       if (lane == 0) epi_ok[warp - 2] = mine ? 1u : 0u;
       epi_barrier();
       const bool all_ok = (epi_ok[0] & epi_ok[1] & epi_ok[2] & epi_ok[3]) != 0u;
       epi_barrier();
       if (!all_ok) { ok = false; break; }
       ptx::tc_fence_after();
-      if (threadIdx.x == 64) RB_TRACE(6);
       const uint32_t t0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * C::kAccCols);
       constexpr int CH = BN >= 32 ? 32 : 16;  // columns per TMEM load
 #pragma unroll 1
@@ -348,7 +357,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
           }
         }
         // here: GATED ? (g = gate product, v = up product) : (v = product)
-        if (SWAP) {
+        if (SWAP && p.reduce) {
+          // this CTA's share of the K range as a float32 slab tile in global memory (it stays in L2); the gated
+          // form keeps two sets of slabs, gate products first
+          const int gn = pt * kBM + lane_row;
+          if (gn < p.n) {
+            const size_t set = (size_t)p.n_split * p.m * p.n;
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+              const int gm = qt * BN + c0 + j;
+              if (gm < p.m) {
+                const size_t at = ((size_t)split * p.m + gm) * p.n + gn;
+                if (GATED) { p.part[at] = g[j]; p.part[set + at] = v[j]; }
+                else p.part[at] = v[j];
+              }
+            }
+          }
+        } else if (SWAP) {
           const int gn = pt * kBM + lane_row;  // output column = weight row
           if (p.part) {
             if (gn < p.n) {
@@ -454,11 +479,135 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
       }
       ptx::tc_fence_before();
       __syncwarp();
-      if (threadIdx.x == 64) RB_TRACE(7);
       if (lane == 0) ptx::mbar_arrive(&acc_empty[as]);
       if (++as == 2) { as = 0; aphase ^= 1u; }
     }
     if (!ok && lane == 0) { p.status[0] = (uint32_t)(-RB_ERR_TIMEOUT); p.status[1] = 0x6E03u; p.status[2] = blockIdx.x; }
+    if (SWAP && p.reduce) {
+      // -------------------------------------------------------------- split-K reduction inside the kernel
+      // Every CTA holds exactly one (tile, split) and all of them are resident at once (the grid is at most one
+      // CTA per SM), so the splits of a tile can wait for one another: each counts itself in when its slab tile
+      // is written, waits (bounded) until all `n_split` have, and then sums ONE slice of the tile's rows out of all
+      // slabs - in split order, so the result does not depend on who finished first - and applies the full
+      // epilogue to that slice.  The last one to finish reading re-arms the tile's counters for the next launch.
+      const int et = threadIdx.x - 64;
+      int pt, qt, split;
+      decode_item(p, blockIdx.x, true, pt, qt, split);
+      const int tile = pt * p.n_q + qt;
+      const int ns = p.n_split;
+      epi_barrier();  // the epilogue threads' slab stores precede thread 0's fence
+      if (et == 0) {
+        bool arrived_all = ok;
+        if (ok) {
+          __threadfence();
+          atomicAdd(p.tile_count + tile, 1u);
+          const long long t0 = clock64();
+          while (ld_acquire_gpu(p.tile_count + tile) < (uint32_t)ns) {
+            if (clock64() - t0 > p.wait_cycles) { arrived_all = false; break; }
+          }
+          if (!arrived_all) { p.status[0] = (uint32_t)(-RB_ERR_TIMEOUT); p.status[1] = 0x6E04u; p.status[2] = blockIdx.x; p.status[3] = (uint32_t)tile; }
+        }
+        epi_ok[0] = arrived_all ? 1u : 0u;
+      }
+      epi_barrier();
+      if (epi_ok[0]) {
+        const int m_eff = min(BN, p.m - qt * BN);
+        const int per = (m_eff + ns - 1) / ns;
+        const int j0 = min(m_eff, split * per), j1 = min(m_eff, j0 + per);
+        const int gn = pt * kBM + lane_row;
+        const bool col_ok = gn < p.n;
+        const float bias = (!GATED && p.bias && col_ok) ? __bfloat162float(p.bias[gn]) : 0.f;
+        const size_t slab = (size_t)p.m * p.n, set = (size_t)ns * slab;
+        uint32_t seq = 0;
+        size_t push_off = 0;
+        if (p.push) {
+          seq = *reinterpret_cast<volatile uint32_t*>(p.tp.seq) + 1u;
+          push_off = ((size_t)(seq & 1u) * p.tp.size + p.tp.rank) * p.tp.slot_elems;
+        }
+        for (int jc = j0; jc < j1; jc += 32) {
+          const int jc1 = min(j1, jc + 32);
+          for (int j = jc; j < jc1; j += 4) {
+            float a[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
+            if (col_ok) {
+              float ta[8][4], tu[GATED ? 8 : 1][4];
+#pragma unroll
+              for (int q = 0; q < 8; ++q)  // every load of this group is in flight before the first sum needs one
+                if (q < ns) {
+#pragma unroll
+                  for (int i = 0; i < 4; ++i)
+                    if (j + i < jc1) {
+                      const size_t at = (size_t)q * slab + (size_t)(qt * BN + j + i) * p.n + gn;
+                      ta[q][i] = __ldcg(p.part + at);
+                      if (GATED) tu[q][i] = __ldcg(p.part + set + at);
+                    }
+                }
+#pragma unroll
+              for (int q = 0; q < 8; ++q)  // split order
+                if (q < ns) {
+#pragma unroll
+                  for (int i = 0; i < 4; ++i)
+                    if (j + i < jc1) { a[i] += ta[q][i]; if (GATED) u[i] += tu[q][i]; }
+                }
+            }
+            if (GATED) {
+              act_inplace(p.act, a);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) a[i] *= u[i];
+            } else {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) a[i] += bias;
+              act_inplace(p.act, a);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              if (j + i < jc1) epi_tile[(j + i - jc) * kEpiPitch + lane_row] = __float2bfloat16_rn(a[i]);
+          }
+          epi_barrier();
+          // 16-byte pieces of output rows: residual, then the store (to every peer's exchange buffer when pushing)
+          for (int id = et; id < (jc1 - jc) * (kBM / 8); id += 128) {
+            const int jj = id / (kBM / 8), c8 = (id % (kBM / 8)) * 8;
+            const int gm = qt * BN + jc + jj, gn8 = pt * kBM + c8;
+            if (gn8 >= p.n) continue;
+            uint4 o = *reinterpret_cast<const uint4*>(epi_tile + jj * kEpiPitch + c8);
+            const size_t at = (size_t)gm * p.n + gn8;
+            if (!GATED && p.residual) {
+              float a8[8], r8[8];
+              unpack8(o, a8);
+              unpack8(*reinterpret_cast<const uint4*>(p.residual + at), r8);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) a8[i] += r8[i];
+              o = pack8(a8);
+            }
+            if (p.push) {
+#pragma unroll
+              for (int r = 0; r < kTpMaxRanks; ++r)
+                if (r < p.tp.size)
+                  *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(const_cast<void*>(p.tp.xbuf[r])) + push_off + at) = o;
+            } else {
+              *reinterpret_cast<uint4*>(p.out + at) = o;
+            }
+          }
+          epi_barrier();  // the staging rows are rewritten by the next chunk; also orders the stores before the fences below
+        }
+        if (et == 0) {
+          // this CTA has read what it needs of the tile's slabs: the last reader re-arms the counters
+          if (atomicAdd(p.tile_done + tile, 1u) == (uint32_t)ns - 1u) { p.tile_count[tile] = 0u; p.tile_done[tile] = 0u; }
+          if (p.push) {
+            // the barrier above orders the epilogue threads' peer stores before this fence; the CTA that is counted
+            // last publishes the sequence number and raises this rank's flag on every peer
+            __threadfence_system();
+            const unsigned int arrived = atomicAdd(p.tp.block_count, 1u);
+            if (arrived == gridDim.x - 1) {
+              *p.tp.block_count = 0u;
+              *reinterpret_cast<volatile uint32_t*>(p.tp.seq) = seq;
+              __threadfence_system();
+              for (int r = 0; r < p.tp.size; ++r)
+                *reinterpret_cast<volatile uint32_t*>(p.tp.flags[r] + (seq & 1u) * kTpMaxRanks + p.tp.rank) = seq;
+            }
+          }
+        }
+      }
+    }
   }
 
   // ------------------------------------------------------------------ teardown
@@ -469,8 +618,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
     // shared memory is released: each full barrier completes when its bytes have arrived.
     volatile uint32_t never = 0;
     const uint32_t issued = issued_count;
-    for (uint32_t i = (issued > (uint32_t)C::kStages ? issued - C::kStages : 0); i < issued; ++i)
-      ptx::mbar_wait(&full_bar[i % C::kStages], (i / C::kStages) & 1u, &never);
+    const uint32_t ns = (uint32_t)n_stages;
+    for (uint32_t i = (issued > ns ? issued - ns : 0); i < issued; ++i)
+      ptx::mbar_wait(&full_bar[i % ns], (i / ns) & 1u, &never, p.wait_cycles);
   }
   __syncthreads();
   if (warp == 1) {
@@ -497,20 +647,19 @@ EncodeTiledFn encode_fn() {
 }
 
 template <int BN, bool SWAP, bool GATED>
-int launch(rb_ctx* ctx, const GemmArgs& a, Params& p) {
+int launch(rb_ctx* ctx, const GemmArgs& a, Params& p, int want_split = 0) {
   using C = Cfg<BN, SWAP, GATED>;
   const void* pbase = SWAP ? a.w : a.x;
   const void* p2base = SWAP ? a.w2 : a.x;
   const void* qbase = SWAP ? a.x : a.w;
   const void* q2base = SWAP ? a.x : a.w2;
-  const CUtensorMap *tp, *tp2, *tq, *tq2;
+  CUtensorMap tp, tp2, tq, tq2;
   RB_TRY(tmap_2d_bf16(ctx, pbase, p.p_rows, a.k, a.k, kBM, &tp));
   RB_TRY(tmap_2d_bf16(ctx, (GATED && SWAP) ? p2base : pbase, p.p_rows, a.k, a.k, kBM, &tp2));
   RB_TRY(tmap_2d_bf16(ctx, qbase, p.q_rows, a.k, a.k, BN, &tq));
   RB_TRY(tmap_2d_bf16(ctx, (GATED && !SWAP) ? q2base : qbase, p.q_rows, a.k, a.k, BN, &tq2));
   p.n_p = (p.p_rows + kBM - 1) / kBM;
   p.n_q = (p.q_rows + BN - 1) / BN;
-  p.n_items = p.n_p * p.n_q * p.n_split;
   auto kern = gemm_tc_kernel<BN, SWAP, GATED>;
   static bool attr_set[64] = {};  // the attribute belongs to the (kernel, device) pair
   const int dv = ctx->device & 63;
@@ -518,47 +667,50 @@ int launch(rb_ctx* ctx, const GemmArgs& a, Params& p) {
     RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
     attr_set[dv] = true;
   }
-  const int grid = std::min(p.n_items, ctx->sm_count);
-  static const bool trace = getenv("RAI_B200_GEMM_TRACE") != nullptr;
-  if (trace) {  // debugging aid: synchronous, prints per-phase timing of this launch
-    unsigned long long* tr = nullptr;
-    RB_CUDA(cudaMalloc(&tr, (size_t)grid * 8 * sizeof(unsigned long long)));
-    RB_CUDA(cudaMemset(tr, 0, (size_t)grid * 8 * sizeof(unsigned long long)));
-    p.trace = tr;
-    RB_CUDA(launch_kernel(kern, dim3((unsigned)grid), dim3(kThreads), (size_t)C::kSmemBytes, ctx->stream, false, *tp, *tp2,
-                          *tq, *tq2, p));
-    RB_CUDA(cudaStreamSynchronize(ctx->stream));
-    std::vector<unsigned long long> h((size_t)grid * 8);
-    RB_CUDA(cudaMemcpy(h.data(), tr, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
-    cudaFree(tr);
-    unsigned long long t0 = ~0ull;
-    for (int c = 0; c < grid; ++c) t0 = std::min(t0, h[c * 8]);
-    double mx[8] = {0}, av[8] = {0};
-    for (int c = 0; c < grid; ++c)
-      for (int i = 0; i < 8; ++i) {
-        const double d = h[c * 8 + i] ? (double)(h[c * 8 + i] - t0) / 1e3 : 0.0;
-        mx[i] = std::max(mx[i], d); av[i] += d / grid;
-      }
-    fprintf(stderr, "gemm_tc<%d,%d,%d> m=%d n=%d k=%d items=%d grid=%d | us since first CTA (avg/max): start %.1f/%.1f  setup %.1f/%.1f  "
-            "prefetched %.1f/%.1f  dep-wait %.1f/%.1f  issued-all %.1f/%.1f  last-mma-commit %.1f/%.1f  epi-begin %.1f/%.1f  epi-end %.1f/%.1f\n",
-            BN, (int)SWAP, (int)GATED, p.m, p.n, p.k, p.n_items, grid, av[0], mx[0], av[1], mx[1], av[2], mx[2], av[3], mx[3], av[4], mx[4],
-            av[5], mx[5], av[6], mx[6], av[7], mx[7]);
+  // Ring depth: as deep as the shared-memory budget allows (decode-sized launches are bound by the bytes they
+  // keep in flight; a shallower ring measured slower even where it lets two kernels share an SM).
+  int stages = C::kStages;
+  if (SWAP) stages = std::max(2, std::min(C::kStages, (int)(ctx->gemm_ring_bytes / C::kStageBytes)));
+  p.stages = stages;
+  const size_t smem = (size_t)stages * C::kStageBytes + 1024;
+  p.wait_cycles = ctx->wait_budget_cycles;
+
+  if (SWAP && want_split >= 1) {
+    // Split-K reduced inside the kernel: one CTA per (tile, split), all resident at once.
+    const int tiles = p.n_p * p.n_q;
+    int s = std::min(want_split, 8);
+    for (; s > 1; --s) {
+      const int per = (p.num_kb + s - 1) / s;
+      if ((p.num_kb + per - 1) / per == s) break;  // no split may be left without K blocks
+    }
+    p.n_split = s;
+    p.kb_per_split = (p.num_kb + s - 1) / s;
+    p.reduce = 1;
+    p.n_items = tiles * s;
+    if (p.n_items > ctx->sm_count || tiles > kGemmMaxReduceTiles)
+      return fail(RB_ERR_INVALID, "GEMM: %d tiles x %d splits exceed one CTA per SM", tiles, s);
+    RB_TRY(gemm_reserve_scratch(ctx, (size_t)(GATED ? 2 : 1) * s * p.m * p.n * sizeof(float)));
+    p.part = ctx->gemm_scratch;
+    p.tile_count = ctx->gemm_tile_count;
+    p.tile_done = ctx->gemm_tile_count + kGemmMaxReduceTiles;
+    RB_CUDA(launch_kernel(kern, dim3((unsigned)p.n_items), dim3(kThreads), smem, ctx->stream, ctx->pdl, tp, tp2, tq, tq2, p));
     ctx->launches++;
     return RB_OK;
   }
-  RB_CUDA(launch_kernel(kern, dim3((unsigned)grid), dim3(kThreads), (size_t)C::kSmemBytes, ctx->stream, ctx->pdl, *tp, *tp2,
-                        *tq, *tq2, p));
+  p.n_items = p.n_p * p.n_q * p.n_split;
+  const int grid = std::min(p.n_items, ctx->sm_count);
+  RB_CUDA(launch_kernel(kern, dim3((unsigned)grid), dim3(kThreads), smem, ctx->stream, ctx->pdl, tp, tp2, tq, tq2, p));
   ctx->launches++;
   return RB_OK;
 }
 
 }  // namespace
 
-int tmap_2d_bf16(rb_ctx* ctx, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows,
-                 const CUtensorMap** out) {
+// The map is copied into the caller's storage: the cache may evict entries at any call.
+int tmap_2d_bf16(rb_ctx* ctx, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, CUtensorMap* out) {
   auto key = std::make_tuple(base, rows, cols, ld, box_rows);
   auto it = ctx->tmaps.find(key);
-  if (it != ctx->tmaps.end()) { *out = &it->second; return RB_OK; }
+  if (it != ctx->tmaps.end()) { *out = it->second; return RB_OK; }
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(RB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld * 2) & 15))
@@ -572,11 +724,14 @@ int tmap_2d_bf16(rb_ctx* ctx, const void* base, int64_t rows, int64_t cols, int6
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(RB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
-  if (ctx->tmaps.size() > 4096) ctx->tmaps.clear();
-  auto ins = ctx->tmaps.emplace(key, tm);
-  *out = &ins.first->second;
+  if (ctx->tmaps.size() >= (size_t)ctx->tmap_cache_limit) ctx->tmaps.clear();
+  ctx->tmaps.emplace(key, tm);
+  *out = tm;
   return RB_OK;
 }
+
+// How many ways to split K for a decode-sized launch that would otherwise leave most SMs idle (1 = do not split).
+int gemm_reserve_scratch(rb_ctx* ctx, size_t bytes);
 
 int gemm_tc_pick_splits(rb_ctx* ctx, int64_t m, int64_t n, int64_t k) {
   if (m > 256) return 1;
@@ -590,6 +745,33 @@ int gemm_tc_pick_splits(rb_ctx* ctx, int64_t m, int64_t n, int64_t k) {
   if (s <= 1) return 1;
   const int64_t per = (num_kb + s - 1) / s;
   return (int)((num_kb + per - 1) / per);
+}
+
+// Splits of a launch that reduces split-K inside the kernel: enough to fill the SMs, at most 8, at least two K
+// blocks each.  0 = this launch does not take that form.  On one GPU the consumer-side reduction (`partials`) is
+// cheaper, so the form is used where something follows the sum inside the same kernel: a push to tensor-parallel
+// peers, or an epilogue the caller asked for (`reduce`).
+static int reduce_splits(rb_ctx* ctx, const GemmArgs& a, int num_kb, bool gated) {
+  if (!(a.push || a.reduce) || a.partials || a.m > 64 || (a.n % 8) != 0) return 0;
+  if (gated && a.push) return 0;
+  const int64_t tiles = (a.n + kBM - 1) / kBM;  // M <= 64: one tile along the rows
+  if (tiles > ctx->sm_count || tiles > kGemmMaxReduceTiles) return 0;
+  int64_t s = std::min<int64_t>(8, ctx->sm_count / tiles);
+  s = std::min<int64_t>(s, std::max<int64_t>(1, num_kb / 2));
+  if (a.push) return (int)std::max<int64_t>(1, s);   // pushing always takes this form, even unsplit
+  if (tiles * 4 >= (int64_t)ctx->sm_count * 3 || s <= 1) return 0;
+  return (int)s;
+}
+
+// Float32 slab space of the in-kernel reduction, grow-only like the attention scratch (captured graphs name it).
+int gemm_reserve_scratch(rb_ctx* ctx, size_t bytes) {
+  if (ctx->gemm_scratch_bytes >= bytes) return RB_OK;
+  float* fresh = nullptr;
+  RB_CUDA(cudaMalloc(&fresh, bytes));
+  if (ctx->gemm_scratch) ctx->retired.push_back(ctx->gemm_scratch);
+  ctx->gemm_scratch = fresh;
+  ctx->gemm_scratch_bytes = bytes;
+  return RB_OK;
 }
 
 int gemm_tc_bf16(rb_ctx* ctx, const GemmArgs& a) {
@@ -615,15 +797,22 @@ int gemm_tc_bf16(rb_ctx* ctx, const GemmArgs& a) {
     p.kb_per_split = (p.num_kb + s - 1) / s;
     p.n_split = s;
   }
+  const int rs = swap ? reduce_splits(ctx, a, p.num_kb, gated) : 0;
+  if (a.push) {
+    RB_REQUIRE(rs >= 1, "GEMM: pushing to tensor-parallel peers needs M <= 64, N %% 8 == 0 and at most one tile per SM");
+    RB_REQUIRE((int64_t)a.n == a.push->slot_elems / kTpMaxRows, "GEMM: the pushed width differs from the exchange buffer's");
+    p.push = 1;
+    p.tp = *a.push;
+  }
   if (swap) {
     p.p_rows = (int)a.n; p.q_rows = (int)a.m;
     if (gated) {
-      if (a.m <= 16) return launch<16, true, true>(ctx, a, p);
-      if (a.m <= 64) return launch<64, true, true>(ctx, a, p);
+      if (a.m <= 16) return launch<16, true, true>(ctx, a, p, rs);
+      if (a.m <= 64) return launch<64, true, true>(ctx, a, p, rs);
       return launch<128, true, true>(ctx, a, p);
     }
-    if (a.m <= 16) return launch<16, true, false>(ctx, a, p);
-    if (a.m <= 64) return launch<64, true, false>(ctx, a, p);
+    if (a.m <= 16) return launch<16, true, false>(ctx, a, p, rs);
+    if (a.m <= 64) return launch<64, true, false>(ctx, a, p, rs);
     if (a.m <= 128) return launch<128, true, false>(ctx, a, p);
     return launch<256, true, false>(ctx, a, p);
   }

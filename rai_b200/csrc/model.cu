@@ -187,7 +187,13 @@ struct rb_model {
   void* xchg_base = nullptr;
   void* peer_base[kTpMaxRanks] = {};
   bool use_exchange = false;
-  bool shard_only = false;  // RAI_B200_SHARD_ONLY=1: run one rank's shard without its peers (timing of per-rank kernels)
+  // RAI_B200_TP_FUSED_PUSH=1: row-parallel GEMMs sum their split-K slabs and push to the peers in their own epilogue
+  // (and sharded gate/up GEMMs apply the gating there).  Off by default: measured slower than the separate
+  // publish / activation kernels, whose many small blocks read the slabs with far more parallelism.
+  bool fused_push = false;
+  // Developer builds only (-DRB_DEBUG_AIDS, a library file of its own): RAI_B200_SHARD_ONLY=1 runs one rank's shard
+  // without its peers to time the per-rank kernels; its outputs are not the model's.  Always false otherwise.
+  bool shard_only = false;
   // One decode step (advance lengths, forward of the tokens in `ids`, argmax back into `ids`)
   // captured as a CUDA graph and replayed; re-captured when the batch or the launch plan changes.
   cudaGraphExec_t step_graph = nullptr;
@@ -226,6 +232,9 @@ void add_param(rb_model* m, const std::string& name, int64_t rows, int64_t cols,
   m->params[name] = std::move(s);
 }
 
+// The exchange is used only when every one of the `tp` ranks voted 1 (the votes arrive summed).
+bool exchange_agreed(float vote_sum, int tp) { return vote_sum > (float)tp - 0.5f; }
+
 int norm_kind(const rb_model* m) {
   return m->cfg.arch == RB_ARCH_PHI2 ? RB_NORM_LAYER : m->cfg.arch == RB_ARCH_GEMMA ? RB_NORM_RMS_ONE_PLUS : RB_NORM_RMS;
 }
@@ -251,6 +260,12 @@ int norm_point(rb_model* m, Pending& pend, const void* w, const void* b, int64_t
   return RB_OK;
 }
 
+// Rows few enough for the GEMM form that sums its split-K slabs inside the kernel and applies the whole epilogue
+// there (used where something must follow the sum at once: the push to tensor-parallel peers, the gating product).
+bool reduce_rows(const rb_model* m, int64_t rows) {
+  return m->fused_push && m->cfg.dtype == RB_BF16 && rows <= 64 && m->ctx->gemm_reduce && !m->ctx->debug_simple_gemm;
+}
+
 bool use_partials(rb_model* m, int64_t rows, int64_t n, int64_t k, int* splits) {
   if (m->cfg.dtype != RB_BF16 || rows > 256) return false;
   const int s = rb_linear_pick_splits(m->ctx, rows, n, k);
@@ -268,8 +283,15 @@ int linear_into_residual(rb_model* m, Pending& pend, const void* x, const void* 
   if (m->cfg.tp_size > 1) {
     // this rank's partial product -> tmp, summed over ranks, folded into the residual by the next norm
     if (m->use_exchange && rows <= kTpMaxRows && n == m->cfg.hidden_size) {
-      // decode-sized: publish into the exchange buffer; the next norm sums the peers' buffers as it reads
-      if (use_partials(m, rows, n, k, &s)) {
+      // decode-sized: the partial product goes into the peers' exchange buffers; the next norm sums them as it reads
+      if (reduce_rows(m, rows) && (n % 8) == 0 && (n + 127) / 128 <= std::min(m->ctx->sm_count, kGemmMaxReduceTiles)) {
+        // the GEMM's own epilogue pushes its tiles and raises the flags: one kernel for product and publish
+        GemmArgs a;
+        a.x = x; a.w = w; a.bias = b; a.m = rows; a.n = n; a.k = k; a.push = &m->peers;
+        ProfScope prof(m->ctx, RB_PROF_GEMM, 2.0 * ((double)n * k + (double)rows * k + (double)rows * n * m->peers.size),
+                       2.0 * rows * n * k);
+        RB_TRY(gemm_tc_bf16(m->ctx, a));
+      } else if (use_partials(m, rows, n, k, &s)) {
         RB_TRY(rb_linear_partials(m->ctx, x, w, m->scratch, rows, n, k, s));
         RB_TRY(tp_publish(m->ctx, m->peers, m->scratch, s, b, nullptr, rows, n));
       } else {
@@ -313,6 +335,16 @@ int mlp_up(rb_model* m, const LayerW& w, int64_t rows) {
   const int64_t fused_items = (m->inter_l + 127) / 128;
   int s = 1;
   if (c.dtype == RB_BF16 && !ctx->debug_simple && rows <= 256 && fused_items * 4 < (int64_t)ctx->sm_count * 3) {
+    if (reduce_rows(m, rows) && (m->inter_l % 8) == 0) {
+      // few weight tiles (a sharded or small intermediate size): split K, sum inside the kernel, activation and
+      // gating product in the same epilogue - one launch where split-K partials plus a finishing kernel took two
+      GemmArgs a;
+      a.x = m->xn; a.w = w.gate; a.w2 = gated ? w.up : nullptr; a.bias = gated ? nullptr : w.fc1_b; a.out = m->act;
+      a.m = rows; a.n = m->inter_l; a.k = H; a.act = c.hidden_act; a.reduce = true;
+      ProfScope prof(ctx, RB_PROF_GEMM, 2.0 * ((gated ? 2.0 : 1.0) * m->inter_l * H + (double)rows * H + (double)rows * m->inter_l),
+                     (gated ? 4.0 : 2.0) * rows * m->inter_l * H);
+      return gemm_tc_bf16(ctx, a);
+    }
     s = rb_linear_pick_splits(ctx, rows, n_all, H);
     if ((size_t)s * rows * n_all <= m->scratch_floats) {
       RB_TRY(rb_linear_partials(ctx, m->xn, w.gate, m->scratch, rows, n_all, H, s));
@@ -483,12 +515,31 @@ extern "C" int32_t rb_model_tp_init(rb_model* m, const void* id, int32_t id_byte
   RB_CUDA(cudaMemcpyAsync(all.data(), stage + sizeof(mine), sizeof(mine) * (size_t)tp, cudaMemcpyDeviceToHost, ctx->stream));
   RB_CUDA(cudaStreamSynchronize(ctx->stream));
   cudaFree(stage);
-  for (int r = 0; r < tp; ++r) {
+  bool opened = true;
+  for (int r = 0; r < tp && opened; ++r) {
     if (r == rank) { m->peer_base[r] = m->xchg_base; continue; }
     cudaError_t e = cudaIpcOpenMemHandle(&m->peer_base[r], all[r], cudaIpcMemLazyEnablePeerAccess);
-    if (e != cudaSuccess) {  // no peer access between these GPUs: stay on NCCL
-      cudaGetLastError();
-      for (int q = 0; q < r; ++q) if (q != rank && m->peer_base[q]) { cudaIpcCloseMemHandle(m->peer_base[q]); m->peer_base[q] = nullptr; }
+    if (e != cudaSuccess) { cudaGetLastError(); m->peer_base[r] = nullptr; opened = false; }
+  }
+  // The ranks decide together: every rank, whether it could map its peers or not, joins ONE sum of "ok" votes, and
+  // the exchange is used only if all voted yes.  (A rank that dropped out on its own would leave the others in a
+  // collective it never joins, and the two sides would then run different protocols.)
+  {
+    float* vote = nullptr;
+    RB_CUDA(cudaMalloc(&vote, sizeof(float)));
+    const float mine_ok = opened ? 1.0f : 0.0f;
+    RB_CUDA(cudaMemcpyAsync(vote, &mine_ok, sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    int nst = nccl().AllReduce(vote, vote, 1, kNcclFloat32, kNcclSum, m->comm, ctx->stream);
+    float total = 0.f;
+    cudaError_t ce = cudaMemcpyAsync(&total, vote, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(ctx->stream);
+    cudaFree(vote);
+    if (nst != 0) return fail(RB_ERR_CUDA, "tensor-parallel set-up: the agreement allreduce failed: %s", nccl().GetErrorString(nst));
+    RB_CUDA(ce);
+    if (!exchange_agreed(total, tp)) {
+      // at least one rank has no peer access: every rank closes what it opened and stays on NCCL
+      for (int q = 0; q < tp; ++q)
+        if (q != rank && m->peer_base[q]) { cudaIpcCloseMemHandle(m->peer_base[q]); m->peer_base[q] = nullptr; }
       return RB_OK;
     }
   }
@@ -505,8 +556,8 @@ extern "C" int32_t rb_model_tp_init(rb_model* m, const void* id, int32_t id_byte
   p.seq = (uint32_t*)local;
   p.block_count = p.seq + 32;
   p.rank = rank; p.size = tp; p.slot_elems = (int64_t)slot_elems;
-  // nobody may publish before every rank has zeroed its region and opened its peers: meet once
-  RB_TRY(allreduce(m, m->tmp, 8));
+  // (the vote above was also the meeting point: no rank publishes before every rank has zeroed its region and
+  // opened its peers)
   RB_CUDA(cudaStreamSynchronize(ctx->stream));
   m->use_exchange = true;
   return RB_OK;
@@ -523,6 +574,7 @@ extern "C" int32_t rb_model_create(rb_ctx* ctx, const rb_model_config* cfg, rb_m
              "rb_model_create: num_attention_heads must divide by num_key_value_heads");
   RB_REQUIRE(c.tp_size >= 1 && c.tp_rank >= 0 && c.tp_rank < c.tp_size, "rb_model_create: bad tensor-parallel rank");
   RB_REQUIRE(c.max_batch > 0 && c.max_seq > 0 && c.max_tokens >= c.max_batch, "rb_model_create: bad capacities");
+  RB_REQUIRE(c.sliding_window >= 0, "rb_model_create: negative sliding_window");
   const int tp = c.tp_size, rank = c.tp_rank;
   const int nq = c.num_attention_heads, nkv = c.num_key_value_heads, G = nq / nkv;
   RB_REQUIRE(c.intermediate_size % tp == 0 && c.vocab_size % tp == 0,
@@ -536,6 +588,8 @@ extern "C" int32_t rb_model_create(rb_ctx* ctx, const rb_model_config* cfg, rb_m
   {
     const char* g = getenv("RAI_B200_GRAPH");  // RAI_B200_GRAPH=0: plain launches for every decode step
     m->use_graph = !(g && g[0] == '0');
+    const char* fp = getenv("RAI_B200_TP_FUSED_PUSH");
+    m->fused_push = fp && fp[0] == '1';
   }
   m->d = c.hidden_size / nq;
   m->es = dtype_size(c.dtype);
@@ -677,6 +731,12 @@ extern "C" int32_t rb_model_create(rb_ctx* ctx, const rb_model_config* cfg, rb_m
   W((size_t)c.max_position_embeddings * half * sizeof(float), (void**)&m->rope_sin);
   if (st == RB_OK) st = rb_rope_tables(ctx, recipe, c.rotary_dim, c.max_position_embeddings, c.rope_theta, m->rope_cos, m->rope_sin);
   if (st == RB_OK) st = rb_kv_cache_create(ctx, c.num_hidden_layers, m->nkv_l, d, c.max_batch, c.max_seq, c.dtype, &m->cache);
+  if (st == RB_OK && c.arch == RB_ARCH_QWEN2 && c.sliding_window > 0) st = rb_kv_cache_set_window(m->cache, c.sliding_window);
+  // split-KV scratch for the worst case (every sequence, 32 splits): a generation then never allocates
+  if (st == RB_OK && c.dtype == RB_BF16)
+    st = attention_reserve_scratch(ctx, (size_t)c.max_batch * m->nq_l * 32 * (d + 2) * sizeof(float));
+  if (st == RB_OK && c.dtype == RB_BF16)  // slabs of the GEMMs that reduce split-K in the kernel: 8 splits, 64 rows, two sets when gated
+    st = gemm_reserve_scratch(ctx, (size_t)2 * 8 * 64 * std::max(m->inter_l, H) * sizeof(float));
   const size_t MT = c.max_tokens;
   W(MT * sizeof(uint32_t), (void**)&m->ids);
   W(MT * H * m->es, &m->h);
@@ -698,6 +758,7 @@ extern "C" int32_t rb_model_create(rb_ctx* ctx, const rb_model_config* cfg, rb_m
     W(m->scratch_floats * sizeof(float), (void**)&m->scratch);
   }
   if (st != RB_OK) { rb_model_destroy(m); return st; }
+#ifdef RB_DEBUG_AIDS
   {
     const char* so = getenv("RAI_B200_SHARD_ONLY");
     m->shard_only = tp > 1 && so && so[0] == '1';
@@ -716,6 +777,7 @@ extern "C" int32_t rb_model_create(rb_ctx* ctx, const rb_model_config* cfg, rb_m
       m->use_exchange = true;
     }
   }
+#endif
   RB_CUDA(cudaStreamSynchronize(ctx->stream));
   *out = m;
   return RB_OK;

@@ -131,7 +131,7 @@ template <typename T>
 __global__ void __launch_bounds__(kPlainAttnWarps * 32)
 attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                        const int32_t* __restrict__ block_table, const int32_t* __restrict__ seq_lens, int pages_per_seq,
-                       int s_new, int q_heads, int kv_heads, int d, float scale, T* __restrict__ out) {
+                       int s_new, int q_heads, int kv_heads, int d, float scale, int window, T* __restrict__ out) {
   __shared__ float sm_m[kPlainAttnWarps], sm_l[kPlainAttnWarps], sm_o[kPlainAttnWarps][256];
   const int m = blockIdx.x, h = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -146,7 +146,10 @@ attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
     o[j] = 0.f;
   }
   float mx = -INFINITY, l = 0.f;
+  const int call_base = seq_lens[b] - s_new;  // first token of this call
   for (int t = warp; t <= limit; t += kPlainAttnWarps) {
+    // sliding window (qwen2.rs:316-334): it acts among the tokens of one call only, the cached prefix stays visible
+    if (t >= call_base && t + window < limit) continue;
     const int page = block_table[(size_t)b * pages_per_seq + t / kPageTokens];
     const size_t off = (((size_t)page * kv_heads + kvh) * kPageTokens + (t % kPageTokens)) * d;
     float dot = 0.f;
@@ -239,11 +242,11 @@ int attention_simple(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, int 
   if (dtype == RB_F32)
     attention_plain_kernel<float><<<grid, warps * 32, 0, ctx->stream>>>(
         (const float*)q, (const float*)c->k + loff, (const float*)c->v + loff, c->block_table, c->seq_lens,
-        c->pages_per_seq, s_new, q_heads, c->kv_heads, c->head_dim, scale, (float*)out);
+        c->pages_per_seq, s_new, q_heads, c->kv_heads, c->head_dim, scale, c->window, (float*)out);
   else if (dtype == RB_BF16)
     attention_plain_kernel<__nv_bfloat16><<<grid, warps * 32, 0, ctx->stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)c->k + loff, (const __nv_bfloat16*)c->v + loff, c->block_table,
-        c->seq_lens, c->pages_per_seq, s_new, q_heads, c->kv_heads, c->head_dim, scale, (__nv_bfloat16*)out);
+        c->seq_lens, c->pages_per_seq, s_new, q_heads, c->kv_heads, c->head_dim, scale, c->window, (__nv_bfloat16*)out);
   else
     return fail(RB_ERR_DTYPE, "attention: dtype %d unsupported", dtype);
   ctx->launches++;

@@ -56,18 +56,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Bounded wait.  `abort_flag` is a shared-memory word any role of the CTA sets when it gives up,
-// so the other roles stop waiting too.  Returns false when the wait was abandoned.
-constexpr long long kWaitBudgetCycles = 2000000000LL;  // about one second at B200 clocks
+// so the other roles stop waiting too.  `budget` is the give-up time in clock cycles (the context's
+// wait budget, about one second by default).  Returns false when the wait was abandoned.
+constexpr long long kDefaultWaitBudgetCycles = 2000000000LL;  // about one second at B200 clocks
 
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          long long budget = kDefaultWaitBudgetCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0x3ffu) == 0) {
+    if ((++spins & 0xffu) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitBudgetCycles) {
+      if (clock64() - t0 > budget) {
         *abort_flag = 1u;
         return false;
       }

@@ -1,0 +1,120 @@
+// Self-test of the give-up path of the bounded device-side waits (rb_selftest_wait_gives_up): kernels whose wait can
+// never be satisfied run with a short budget, and the host checks that they returned, that the status word
+// names them, and that nothing else was written.  Nothing here faults, traps or spins without bound.
+#include <vector>
+
+#include "ctx.h"
+#include "ptx.cuh"
+
+namespace rb {
+namespace {
+
+// One thread waits, with the library's own helper, on an mbarrier that expects an arrival nobody makes.
+__global__ void wait_probe_kernel(long long budget, uint32_t* status, uint32_t* returned) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ volatile uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(&bar, 1);
+    abort_flag = 0;
+    ptx::fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const bool ok = ptx::mbar_wait(&bar, 0u, &abort_flag, budget);
+    if (!ok) { status[0] = (uint32_t)(-RB_ERR_TIMEOUT); status[1] = 0x5E1Fu; status[2] = blockIdx.x; status[3] = 0u; }
+    *returned = ok ? 2u : 1u;
+  }
+}
+
+struct DevBuf {
+  void* p = nullptr;
+  ~DevBuf() { if (p) cudaFree(p); }
+};
+
+int read_status(rb_ctx* ctx, uint32_t* w) {
+  RB_CUDA(cudaStreamSynchronize(ctx->stream));
+  RB_CUDA(cudaMemcpy(w, ctx->status_dev, 4 * sizeof(uint32_t), cudaMemcpyDeviceToHost));
+  RB_CUDA(cudaMemset(ctx->status_dev, 0, 4 * sizeof(uint32_t)));
+  return RB_OK;
+}
+
+}  // namespace
+}  // namespace rb
+
+using namespace rb;
+
+extern "C" int32_t rb_selftest_wait_gives_up(rb_ctx* ctx, int32_t which, int64_t budget_us) {
+  RB_REQUIRE(ctx, "rb_selftest_wait_gives_up: null context");
+  RB_REQUIRE(which == 0 || which == 1, "rb_selftest_wait_gives_up: unknown test %d", which);
+  RB_REQUIRE(budget_us >= 1 && budget_us <= 1000000, "rb_selftest_wait_gives_up: budget %lld us outside [1, 1 000 000]",
+             (long long)budget_us);
+  RB_TRY(rb_sync(ctx));  // start from a clear status word
+  const long long budget = (long long)((double)budget_us * ctx->cycles_per_us);
+  uint32_t w[4];
+  if (which == 0) {
+    DevBuf ret;
+    RB_CUDA(cudaMalloc(&ret.p, sizeof(uint32_t)));
+    RB_CUDA(cudaMemsetAsync(ret.p, 0, sizeof(uint32_t), ctx->stream));
+    wait_probe_kernel<<<1, 32, 0, ctx->stream>>>(budget, ctx->status_dev, (uint32_t*)ret.p);
+    RB_CUDA(cudaGetLastError());
+    ctx->launches++;
+    RB_TRY(read_status(ctx, w));
+    uint32_t returned = 0;
+    RB_CUDA(cudaMemcpy(&returned, ret.p, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    if (returned != 1u || w[0] != (uint32_t)(-RB_ERR_TIMEOUT) || w[1] != 0x5E1Fu)
+      return fail(RB_ERR_CUDA, "wait self-test: expected a recorded give-up at 0x5E1F, got returned=%u status={%u, 0x%x}",
+                  returned, w[0], w[1]);
+    return RB_OK;
+  }
+  // ---- the tensor-parallel norm over a two-member group that lives entirely in this GPU's memory
+  const int rows = 2, hidden = 256;
+  DevBuf region, x, wt, out, sum;
+  const size_t slot_elems = (size_t)kTpMaxRows * hidden;
+  const size_t region_bytes = 512 + 2 * 2 * slot_elems * 2;
+  RB_CUDA(cudaMalloc(&region.p, region_bytes));
+  RB_CUDA(cudaMalloc(&x.p, (size_t)rows * hidden * 2));
+  RB_CUDA(cudaMalloc(&wt.p, (size_t)hidden * 2));
+  RB_CUDA(cudaMalloc(&out.p, (size_t)rows * hidden * 2));
+  RB_CUDA(cudaMalloc(&sum.p, (size_t)rows * hidden * 2));
+  RB_CUDA(cudaMemsetAsync(region.p, 0, region_bytes, ctx->stream));
+  RB_CUDA(cudaMemsetAsync(x.p, 0, (size_t)rows * hidden * 2, ctx->stream));
+  std::vector<uint16_t> ones((size_t)hidden, 0x3F80u);  // bf16 1.0
+  RB_CUDA(cudaMemcpyAsync(wt.p, ones.data(), (size_t)hidden * 2, cudaMemcpyHostToDevice, ctx->stream));
+  RB_CUDA(cudaMemsetAsync(out.p, 0x5A, (size_t)rows * hidden * 2, ctx->stream));
+  RB_CUDA(cudaMemsetAsync(sum.p, 0x5A, (size_t)rows * hidden * 2, ctx->stream));
+  TpPeers tp{};
+  uint32_t* flags = (uint32_t*)region.p;          // [2 slots][kTpMaxRanks]
+  tp.flags[0] = tp.flags[1] = flags;
+  tp.xbuf[0] = tp.xbuf[1] = (const char*)region.p + 512;
+  tp.seq = flags + 64;                             // exchange number 1 has been "published" by member 0 only
+  tp.block_count = flags + 96;
+  tp.rank = 0; tp.size = 2; tp.slot_elems = (int64_t)slot_elems;
+  const uint32_t one = 1u;
+  RB_CUDA(cudaMemcpyAsync(tp.seq, &one, sizeof(one), cudaMemcpyHostToDevice, ctx->stream));
+  RB_CUDA(cudaMemcpyAsync(flags + 1 * kTpMaxRanks + 0, &one, sizeof(one), cudaMemcpyHostToDevice, ctx->stream));
+  RB_CUDA(cudaStreamSynchronize(ctx->stream));  // `ones` and `one` are read by the copies above
+  const long long keep = ctx->wait_budget_cycles;
+  ctx->wait_budget_cycles = budget;
+  int st = norm_tp(ctx, tp, RB_NORM_RMS, x.p, wt.p, nullptr, 1e-6f, rows, hidden, out.p, sum.p);
+  ctx->wait_budget_cycles = keep;
+  RB_TRY(st);
+  RB_TRY(read_status(ctx, w));
+  std::vector<uint16_t> got((size_t)rows * hidden);
+  RB_CUDA(cudaMemcpy(got.data(), out.p, got.size() * 2, cudaMemcpyDeviceToHost));
+  bool untouched = true;
+  for (uint16_t v : got) untouched = untouched && v == 0x5A5Au;
+  if (w[0] != (uint32_t)(-RB_ERR_TIMEOUT) || w[1] != 0x7A11u || !untouched)
+    return fail(RB_ERR_CUDA, "exchange-wait self-test: expected a give-up at 0x7A11 with the outputs untouched, got status={%u, 0x%x}, "
+                "outputs %s", w[0], w[1], untouched ? "untouched" : "written");
+  // the same call once the second member has raised its flag: completes, nothing recorded
+  RB_CUDA(cudaMemcpy(flags + 1 * kTpMaxRanks + 1, &one, sizeof(one), cudaMemcpyHostToDevice));
+  RB_TRY(norm_tp(ctx, tp, RB_NORM_RMS, x.p, wt.p, nullptr, 1e-6f, rows, hidden, out.p, sum.p));
+  RB_TRY(read_status(ctx, w));
+  RB_CUDA(cudaMemcpy(got.data(), out.p, got.size() * 2, cudaMemcpyDeviceToHost));
+  bool written = true;
+  for (uint16_t v : got) written = written && v == 0u;  // norm of an all-zero row is zero
+  if (w[0] != 0u || !written)
+    return fail(RB_ERR_CUDA, "exchange-wait self-test: the healthy call after the give-up failed (status %u, outputs %s)", w[0],
+                written ? "written" : "not written");
+  return RB_OK;
+}
