@@ -52,6 +52,9 @@ def parse_args():
     ap.add_argument("--shard-of", type=int, default=0,
                     help="developer aid: time ONE rank's shard of an N-way tensor-parallel model on one GPU, without its "
                          "peers (results are not the model's outputs; the line is labelled)")
+    ap.add_argument("--skip-parity", action="store_true", help="skip the oracle comparison that follows the timed region")
+    ap.add_argument("--skip-other-configs", action="store_true",
+                    help="skip the short decode runs of the other benchmark configurations (single-GPU default run only)")
     ap.add_argument("--skip-fill", action="store_true",
                     help="leave the KV cache zero-filled instead of prefilling it (same traffic; for profiler runs)")
     return ap.parse_args()
@@ -146,31 +149,35 @@ def prefill_flops(cfg, batch, seq):
 # --------------------------------------------------------------------------------------------------
 # CPU arm: the oracle on the host cores, bounded sample
 # --------------------------------------------------------------------------------------------------
-def cpu_decode_sample(cfg, batch, ctx, steps, warmup):
+def cpu_decode_sample(cfg, batch, ctx, steps, warmup, params=None):
     """Times the CPU restatement on a bounded sample of the same workload: the full-width model with
-    1 and 2 layers, batch `batch`, a `ctx`-token cache injected as random K/V, `steps` decode steps
-    each.  Per-layer and outside-the-layers times are separated by the difference and extrapolated
-    to the full depth."""
+    1 and 2 layers, batch `batch`, a `ctx`-token cache injected as random K/V, `steps` (>= 5) decode steps
+    each after `warmup` untimed ones.  Per-layer and outside-the-layers times are separated by the difference of the
+    two medians and extrapolated to the full depth; the spread of the step times is reported with the figure."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import torch
     import adapter
     import rai_cpu
     from rai_b200 import configs, synth
 
+    steps = max(5, int(steps))
+    warmup = max(1, int(warmup))
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     g = torch.Generator().manual_seed(1234)
     full_layers = cfg["num_hidden_layers"]
     cfg2 = dict(cfg, num_hidden_layers=2, max_position_embeddings=ctx + steps + warmup + 8)
-    params = {}
-    for name, shape, kind in synth.param_shapes(cfg2):
-        if kind == "norm_w":
-            params[name] = torch.ones(shape)
-        else:
-            params[name] = torch.randn(shape, generator=g) * 0.02
+    if params is None:
+        params = {}
+        for name, shape, kind in synth.param_shapes(cfg2):
+            if kind == "norm_w":
+                params[name] = torch.ones(shape)
+            else:
+                params[name] = torch.randn(shape, generator=g) * 0.02
     nkv = cfg.get("num_key_value_heads") or cfg["num_attention_heads"]
     d = configs.head_dim(cfg)
-    times = {}
+    times, all_ts = {}, {}
+    t_wall = time.perf_counter()
     for n_layers in (1, 2):
         c = dict(cfg2, num_hidden_layers=n_layers)
         model = rai_cpu.build(adapter.oracle_config(c), adapter.oracle_params(c, params))
@@ -185,16 +192,21 @@ def cpu_decode_sample(cfg, batch, ctx, steps, warmup):
             if i >= warmup:
                 ts.append(time.perf_counter() - t0)
         times[n_layers] = statistics.median(ts)
+        all_ts[n_layers] = ts
         del model
+    wall = time.perf_counter() - t_wall
     per_layer = max(times[2] - times[1], 1e-9)
     outside = max(times[1] - per_layer, 0.0)
     step_s = outside + full_layers * per_layer
+    spread = {n: {"min_ms": min(v) * 1e3, "median_ms": statistics.median(v) * 1e3, "max_ms": max(v) * 1e3} for n, v in all_ts.items()}
+    n_run = 2 * (steps + warmup)
     return {"value": batch / step_s, "unit": "tok/s", "cores": cores, "kind": "port",
             "sample": (f"torch-CPU float32 restatement of rai's Cpu path, full-width {cfg['arch']} layers: 1- and 2-layer "
-                       f"models, batch {batch}, {ctx}-token cache injected, {steps} decode steps each (median); "
-                       f"per-layer {per_layer * 1e3:.0f} ms, outside layers {outside * 1e3:.0f} ms, extrapolated to "
-                       f"{full_layers} layers = {step_s:.2f} s/step"),
-            "ms_per_step": step_s * 1e3}
+                       f"models, batch {batch}, {ctx}-token cache injected, {steps} timed decode steps each (median) after "
+                       f"{warmup} warm-up; per-layer {per_layer * 1e3:.0f} ms, outside layers {outside * 1e3:.0f} ms, "
+                       f"extrapolated to {full_layers} layers = {step_s:.2f} s/step"),
+            "ms_per_step": step_s * 1e3, "extrapolated": True, "sample_steps_run": n_run,
+            "sample_ms_per_step": wall / n_run * 1e3, "sample_wall_s": wall, "spread": spread}
 
 
 def decode_timeline(model, dev, rewind, first, T0, path=None, steps=4):
@@ -235,7 +247,14 @@ def decode_timeline(model, dev, rewind, first, T0, path=None, steps=4):
     return out
 
 
+CPU_SAMPLE_STEPS, CPU_SAMPLE_WARMUP = 6, 1   # the same sample in the GPU arm's cpu_baseline and in the reference arm
+
+
 def run_reference(args):
+    """The reference arm: rai's Cpu path (its op-for-op restatement; rai itself cannot be built here) on the host
+    cores.  Every "step" it runs is one decode step of a bounded sample (full-width 1- and 2-layer models); the
+    line's `steps` and `ms_per_step` describe exactly what ran, so that steps x ms_per_step is this run's own
+    time, and `value` is the tokens/s extrapolated to the full depth (`extrapolated: true`)."""
     from rai_b200 import configs
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -243,19 +262,22 @@ def run_reference(args):
     cfg = configs.get(args.config)
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
-    steps, warmup = max(1, min(args.steps, 3)), max(1, min(args.warmup, 1))
     t0 = time.perf_counter()
-    base = cpu_decode_sample(cfg, args.decode_batch, args.context, steps, warmup)
+    base = cpu_decode_sample(cfg, args.decode_batch, args.context, CPU_SAMPLE_STEPS, CPU_SAMPLE_WARMUP)
     line = {
         "impl": "reference", "metric": "decode_tokens_per_s", "value": base["value"], "unit": "tok/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
+        "n_gpus": args.gpus, "steps": base["sample_steps_run"], "warmup": 0, "ms_per_step": base["sample_ms_per_step"],
+        "requested_steps": args.steps, "requested_warmup": args.warmup,
+        "extrapolated": True, "full_depth_ms_per_step": base["ms_per_step"],
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args, cfg, args.gpus),
-        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample", "spread")},
         "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "wall_s": time.perf_counter() - t0,
         "note": ("rai's Cpu (candle) path cannot be built in this environment (no Rust toolchain); this is its "
-                 f"op-for-op restatement timed on {base['cores']} host threads, {steps} sample step(s) per model"),
+                 f"op-for-op restatement timed on {base['cores']} host threads.  `steps` and `ms_per_step` are the sample "
+                 "steps actually run (1- and 2-layer full-width models) and their mean duration; `value` extrapolates the "
+                 "per-layer time to the full depth"),
     }
     print(json.dumps(line), flush=True)
 
@@ -266,6 +288,30 @@ def workload_config(args, cfg, n):
             "layers": cfg["num_hidden_layers"], "decode_batch": args.decode_batch, "context": args.context,
             "prefill_batch": args.prefill_batch, "prefill_len": args.prefill_len,
             "parallelism": f"tp{n}", "l2": "inputs larger than L2 (>= 14 GB of weights and KV streamed per step)"}
+
+
+OTHER_CONFIGS = [  # (name, decode batch, context): configurations 1-4 of the benchmark definition
+    ("qwen2-0.5b", 1, 128), ("phi2", 8, 512), ("phi3-mini", 4, 2048), ("gemma-2b", 32, 1024)]
+
+
+def other_configs():
+    """Decode ms/step and whole-step roofline fraction of the other benchmark configurations: a short run of this
+    same script per configuration, each in a process of its own."""
+    out = {}
+    for name, batch, ctx in OTHER_CONFIGS:
+        cmd = [sys.executable, os.path.abspath(__file__), "--config", name, "--decode-batch", str(batch), "--context", str(ctx),
+               "--steps", "24", "--warmup", "3", "--profile-steps", "1", "--skip-cpu", "--skip-e2e", "--skip-prefill",
+               "--skip-timeline", "--skip-parity", "--skip-other-configs"]
+        try:
+            r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+            d = json.loads(r.stdout.strip().splitlines()[-1])
+            out[name] = {"decode_batch": batch, "context": ctx, "ms_per_step": d["ms_per_step"], "tok_s": d["value"],
+                         "frac_of_measured_copy": d["roofline"]["whole_step"]["frac_of_measured_copy"],
+                         "frac_of_nominal_8tbs": d["roofline"]["whole_step"]["frac_of_nominal_8tbs"],
+                         "graph": d["decode_step_is_cuda_graph"]}
+        except Exception as e:
+            out[name] = {"error": f"{type(e).__name__}: {e}"}
+    return out
 
 
 # --------------------------------------------------------------------------------------------------
@@ -391,7 +437,7 @@ def run_ours(args):
     PK = max(1, min(args.profile_steps, K))
     rewind(T0)
     _lib.call("rb_profile_start", dev.ctx)
-    model.decode_loop(first, T0, PK)
+    plain_tokens = model.decode_loop(first, T0, PK)   # launch by launch (profiling switches the captured step off)
     for i, cname in enumerate(classes):
         out4 = (ctypes.c_double * 4)()
         _lib.call("rb_profile_read", dev.ctx, i, out4)
@@ -400,6 +446,8 @@ def run_ours(args):
                            "gbytes_per_step": out4[2] / PK / 1e9, "avg_launch_us": out4[1] / out4[0] * 1e3,
                            "achieved_gbs": out4[2] / 1e9 / (out4[1] / 1e3) if out4[1] > 0 else None}
     dev.synchronize()
+    # the captured, replayed step and the launch-by-launch step must produce the same tokens
+    graph_equals_plain = bool(torch.equal(plain_tokens, out_tokens[:PK]))
 
     # ---- the same steps as the device ran them (graph replay, overlap included): a tracing pass of its own
     # (single GPU only: the decode steps of a tensor-parallel group are collective, so a pass that one rank runs
@@ -483,20 +531,24 @@ def run_ours(args):
     step_bytes = 0.5 * (bytes_first + bytes_last)
     step_gbs = step_bytes / 1e9 / (decode_ms / K / 1e3)
     gemm = prof.get("gemm", {})
+    # The dominant kernel class, per GPU: rank 0's launches over rank 0's shard against ONE GPU's peak.
+    profiled_case = world == 1 and args.config == "qwen2-7b" and B == 64
     roofline = {
         "bound": "hbm", "kernel": "gemm_tc_kernel (weight-streaming tcgen05 GEMM; all Linear layers of a decode step)",
-        "achieved": gemm.get("achieved_gbs"), "peak": peaks["hbm_gbs"] * world, "unit": "GB/s",
-        "frac": (gemm["achieved_gbs"] / (peaks["hbm_gbs"] * world)) if gemm.get("achieved_gbs") else None,
-        "peak_kind": f"{peak_kind} stream-copy bandwidth x {world} GPU(s)",
-        # DRAM bytes per launch: ncu (profiles/gemm_tc_decode_2layer_b64.md) measured 478.6 MB of DRAM
-        # read+write for the four GEMMs of one layer against 486.2 MB of algorithmic bytes (the float32
-        # split-K partials mostly stay in L2), i.e. 0.98 of algorithmic; scaled to this run's launches.
-        "traffic": (0.98 * gemm["gbytes_per_step"] * 1e9 / gemm["launches_per_step"]) if gemm else None,
-        "traffic_unit": "bytes per launch (ncu on a 2-layer case, scaled by algorithmic bytes)",
+        "achieved": gemm.get("achieved_gbs"), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+        "frac": (gemm["achieved_gbs"] / peaks["hbm_gbs"]) if gemm.get("achieved_gbs") else None,
+        "peak_kind": f"{peak_kind} stream-copy bandwidth of one GPU; achieved is rank 0's own launches over its own shard",
+        # DRAM bytes per launch are not measured by this run: ncu measured 478.6 MB of DRAM read+write for the four
+        # GEMMs of one layer against 486.2 MB of algorithmic bytes (0.98; the float32 split-K partials mostly stay in
+        # L2) on the 2-layer single-GPU case of the summary named below.  Given for that configuration only.
+        "traffic": (0.98 * gemm["gbytes_per_step"] * 1e9 / gemm["launches_per_step"]) if (gemm and profiled_case) else None,
+        "traffic_source": ("profiles/gemm_tc_decode_2layer_b64.md (ncu dram__bytes_read+write on a 2-layer case, 0.98 of "
+                           "algorithmic, scaled by this run's algorithmic bytes per launch)") if profiled_case else None,
         "algorithmic_bytes_per_launch": (gemm["gbytes_per_step"] * 1e9 / gemm["launches_per_step"]) if gemm else None,
         "avg_launch_us": gemm.get("avg_launch_us"), "launches_per_step": gemm.get("launches_per_step"),
         "algorithmic_gbytes_per_step": gemm.get("gbytes_per_step"),
-        "whole_step": {"algorithmic_gbytes": step_bytes / 1e9, "achieved_gbs": step_gbs,
+        # the whole model's algorithmic bytes per step over the whole job's time, against N GPUs' bandwidth
+        "whole_step": {"algorithmic_gbytes": step_bytes / 1e9, "achieved_gbs": step_gbs, "gpus": world,
                        "frac_of_measured_copy": step_gbs / (peaks["hbm_gbs"] * world),
                        "frac_of_nominal_8tbs": step_gbs / (NOMINAL_HBM_GBS * world)},
         "per_class": prof,
@@ -510,17 +562,40 @@ def run_ours(args):
             "method": "CUDA activity records of the replayed step; per kernel: its end minus the latest end before it",
             "span_us_per_step": in_graph["span_us_per_step"], "gemm_advance_us_per_step": adv,
             "gemm_achieved_gbs": (gemm["gbytes_per_step"] * 1e6 / adv) if adv > 0 else None,
-            "gemm_frac": (gemm["gbytes_per_step"] * 1e6 / adv / (peaks["hbm_gbs"] * world)) if adv > 0 else None,
+            "gemm_frac": (gemm["gbytes_per_step"] * 1e6 / adv / peaks["hbm_gbs"]) if adv > 0 else None,
             "per_kernel_per_step": in_graph["per_kernel_per_step"]}
     elif in_graph:
         roofline["in_graph"] = in_graph
     if prefill:
         prefill["frac_of_measured_sustained_bf16"] = prefill["tflops"] / (peaks["bf16_tflops_sustained"] * world)
         prefill["frac_of_nominal_bf16"] = prefill["tflops"] / (NOMINAL_BF16_TFLOPS * world)
-    cpu = None
-    if world == 1 and not args.skip_cpu:
-        base = cpu_decode_sample(cfg, B, T0, 2, 1)
-        cpu = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    # ---- after the timed region: the CPU arm and the oracle comparison share one set of 2-layer full-width weights
+    cpu, parity = None, {"graph_replay_equals_plain_launch_tokens": graph_equals_plain, "steps_compared": PK}
+    if world == 1 and (not args.skip_cpu or not args.skip_parity):
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import parity_kit
+        cfg2 = dict(cfg, num_hidden_layers=min(2, cfg["num_hidden_layers"]))
+        cfg2["max_position_embeddings"] = max(cfg2["max_position_embeddings"], T0 + 64)
+        params2 = parity_kit.rounded_params(cfg2, 4321)
+        if not args.skip_parity:
+            # the timed shape (batch, context) on a 2-layer model of the same widths, from an injected cache, through the
+            # same entry points, against the oracle: logits within 2e-2 of the logit range, greedy tokens equal except at
+            # reference near-ties
+            pm = Model(cfg2, _lib.BF16, dev, B, T0 + 16, B)
+            for k, v in params2.items():
+                pm.update_param(k, v)
+            pm.finalize()
+            parity.update(parity_kit.decode_parity(cfg2, params2, pm, B, T0, 2, 4322))
+            parity["ok"] = bool(graph_equals_plain and parity["max_logit_err_of_range"] <= parity["tolerance"]
+                                and parity["of_which_not_near_ties"] == 0)
+            pm.close()
+        if not args.skip_cpu:
+            base = cpu_decode_sample(cfg, B, T0, CPU_SAMPLE_STEPS, CPU_SAMPLE_WARMUP, params=params2)
+            cpu = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample", "spread")}
+        del params2
+    other = None
+    if world == 1 and not args.skip_other_configs and args.config == "qwen2-7b" and not args.layers and not args.shard_of:
+        other = other_configs()
     line = {
         "metric": "decode_tokens_per_s", "value": decode_tok_s, "unit": "tok/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": decode_ms / K, "higher_is_better": True, "scaling": "strong",
@@ -530,6 +605,7 @@ def run_ours(args):
         "decode_step_is_cuda_graph": graph_active,
         "shard_only_of": args.shard_of or None,
         "tokens_checksum": int(out_tokens.to(torch.int64).sum().item()),
+        "parity_checked": parity, "other_configs": other,
     }
     print(json.dumps(line), flush=True)
     if dist is not None:

@@ -16,6 +16,7 @@
 #include <stdlib.h>
 
 #include <algorithm>
+#include <mutex>
 
 #include "ctx.h"
 #include "ptx.cuh"
@@ -629,12 +630,15 @@ int launch_attention(rb_ctx* ctx, rb_kv_cache* c, AParams& p, int batch, int max
 // an error, or a serving loop that cannot afford the device-wide synchronisation an allocation may
 // imply.  For them the same kernels run here with the partials in a fixed array that is part of
 // the library image: every GPU that loads the library holds these 4 MiB until the process exits.
+// (What the entry point cannot rule out is the CUDA runtime loading a kernel's code on its first
+// launch; a caller whose pool takes all remaining memory makes one call per head size first.)
 // ------------------------------------------------------------------------------------------
 constexpr size_t kStaticScratchFloats = 1u << 20;  // 4 MiB
 static __device__ __align__(256) float g_static_attn_scratch[kStaticScratchFloats];
 // In host code the array's name is only a handle for the runtime, not a device address: the address
 // the kernels need is asked for once per device (with that device current) and kept here.
 static float* g_static_attn_scratch_dev[64] = {};
+static std::mutex g_static_attn_scratch_lock;
 
 template <int D>
 static int launch_attention_decode_static(rb_ctx* ctx, rb_kv_cache* c, AParams& p, int batch, int max_len, float* scratch) {
@@ -787,16 +791,21 @@ extern "C" int32_t rb_attention_decode_static(rb_ctx* ctx, const void* q, rb_kv_
     RB_REQUIRE(c->host_lens[b] >= 1, "rb_attention_decode_static: sequence %d is empty", b);
     max_len = std::max(max_len, c->host_lens[b]);
   }
-  // One-time set-up per device, done by the first call on it: turn the symbol into a device address.
-  if (!g_static_attn_scratch_dev[ctx->device]) {
-    int current = -1;
-    RB_CUDA(cudaGetDevice(&current));
-    RB_REQUIRE(current == ctx->device, "rb_attention_decode_static: device %d must be current (it is %d)", ctx->device, current);
-    float* ptr = nullptr;
-    RB_CUDA(cudaGetSymbolAddress((void**)&ptr, g_static_attn_scratch));
-    g_static_attn_scratch_dev[ctx->device] = ptr;
+  // One-time set-up per device, done by the first call on it: turn the symbol into a device address.  The lock
+  // makes first calls from several host threads safe (the table is read and filled under it).
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> guard(g_static_attn_scratch_lock);
+    if (!g_static_attn_scratch_dev[ctx->device]) {
+      int current = -1;
+      RB_CUDA(cudaGetDevice(&current));
+      RB_REQUIRE(current == ctx->device, "rb_attention_decode_static: device %d must be current (it is %d)", ctx->device, current);
+      float* ptr = nullptr;
+      RB_CUDA(cudaGetSymbolAddress((void**)&ptr, g_static_attn_scratch));
+      g_static_attn_scratch_dev[ctx->device] = ptr;
+    }
+    scratch = g_static_attn_scratch_dev[ctx->device];
   }
-  float* scratch = g_static_attn_scratch_dev[ctx->device];
   AParams p{};
   const size_t loff = (size_t)layer * c->layer_stride_elems();
   p.q = (const bf16*)q;

@@ -92,3 +92,23 @@ def test_baseline_config_sizes():
     assert abs(count("qwen2-7b") * 2 / 1e9 - 15.23) < 0.05      # 14.14 GB streamed + 1.09 GB embedding table
     assert abs(count("qwen2-0.5b") * 2 / 1e9 - 0.988) < 0.01
     assert abs(count("gemma-2b") * 2 / 1e9 - 5.012) < 0.02
+
+
+def test_rust_shim_declares_every_export():
+    """integration/b200.rs carries an `extern "C"` block generated from the header: it must be exactly what the
+    generator emits now (so it lists every entry point with the header's own types) and every library call the shim
+    makes must be one of them."""
+    import importlib.util
+    import os
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("gen_ffi", os.path.join(root, "integration", "gen_ffi.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    src = open(os.path.join(root, "integration", "b200.rs")).read()
+    block = src[src.index("// <ffi>\n") + len("// <ffi>\n"):src.index("// </ffi>")]
+    assert block == gen.emit(), "run `python integration/gen_ffi.py --write`"
+    declared = set(re.findall(r"pub fn (rb_\w+)\(", block))
+    assert declared == set(_lib.parse_header())
+    used = set(re.findall(r"\b(rb_[a-z0-9_]+)\(", src[src.index("// </ffi>"):]))
+    assert used <= declared, used - declared

@@ -25,6 +25,10 @@ def test_reference_arm_prints_one_json_line_with_the_contract_keys():
     assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["value"] == d["value"]
     assert d["e2e"]["value"] == d["value"] and d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["d2h_bytes_per_step"] == 0
     assert "workload" in d["config"] and "model" not in d["config"]
+    # the line describes what actually ran: the sample steps and their mean duration, flagged as extrapolated
+    assert d["extrapolated"] is True and d["steps"] >= 10 and d["full_depth_ms_per_step"] > 0
+    assert d["steps"] * d["ms_per_step"] / 1e3 <= d["wall_s"] + 0.5
+    assert "spread" in d["cpu_baseline"]
 
 
 def test_other_ranks_of_the_reference_arm_exit_quietly():
