@@ -83,3 +83,63 @@ def shard_weights(cfg: dict, weights: Dict[str, np.ndarray], p: Plan) -> Dict[st
         else:
             out[name] = w
     return out
+
+
+# --------------------------------------------------------------------------------------------------
+# Host-side agreement and liveness of a tensor-parallel group (torch.distributed; no GPU involved)
+# --------------------------------------------------------------------------------------------------
+def agree_on_exchange(local_ok: bool, group=None) -> bool:
+    """The decision rb_model_tp_init takes about its peer-memory exchange, stated on the host: every rank, whether
+    it could map its peers' buffers or not, joins ONE sum of votes, and the exchange is used only if all voted yes.
+    A rank that dropped out on its own would leave the others in a collective it never joins, and the two sides
+    would go on with different protocols."""
+    import torch
+    import torch.distributed as dist
+    vote = torch.tensor([1.0 if local_ok else 0.0])
+    dist.all_reduce(vote, op=dist.ReduceOp.SUM, group=group)
+    return bool(vote.item() > dist.get_world_size(group) - 0.5)
+
+
+class PeerLeft(RuntimeError):
+    """A member of the tensor-parallel group has announced that it leaves, or has gone silent."""
+
+
+class PeerWatch:
+    """Liveness of a tensor-parallel group between decode steps, through a key-value store (torch.distributed's
+    TCPStore / the default store).  A decode step of a group is collective: a rank that launched it while a peer is
+    gone would wait on that peer's flags until the device-side budget runs out.  So every rank posts the step it is
+    about to run, a rank that leaves says so first (between steps, with none of its kernels in flight), and `check`
+    is called before each launch: it raises PeerLeft instead of launching when a peer has left or has not reached
+    this step within `timeout_s`."""
+
+    def __init__(self, store, rank: int, size: int, timeout_s: float = 5.0):
+        self.store, self.rank, self.size, self.timeout_s = store, rank, size, timeout_s
+
+    def post(self, step: int) -> None:
+        self.store.set(f"tp/step/{self.rank}", str(int(step)))
+
+    def leave(self) -> None:
+        self.store.set(f"tp/left/{self.rank}", "1")
+
+    def _get(self, key: str):
+        try:
+            return self.store.get(key).decode() if self.store.check([key]) else None
+        except Exception:
+            return None
+
+    def check(self, step: int) -> None:
+        import time
+        deadline = time.time() + self.timeout_s
+        self.post(step)
+        for r in range(self.size):
+            if r == self.rank:
+                continue
+            while True:
+                if self._get(f"tp/left/{r}") is not None:
+                    raise PeerLeft(f"rank {r} left the group before step {step}")
+                at = self._get(f"tp/step/{r}")
+                if at is not None and int(at) >= step:
+                    break
+                if time.time() > deadline:
+                    raise PeerLeft(f"rank {r} did not reach step {step} within {self.timeout_s} s")
+                time.sleep(0.005)

@@ -18,6 +18,6 @@ def test_tensor_parallel_matches_oracle(world):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(29600 + world), os.path.join(HERE, "tp_check.py")]
-    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=1500)
     sys.stdout.write(r.stdout[-3000:])
     assert r.returncode == 0, r.stderr[-3000:]

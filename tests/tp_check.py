@@ -30,12 +30,20 @@ def main():
     cases = [("tiny-qwen2", _lib.F32, 1e-4), ("tiny-qwen2", _lib.BF16, 2e-2), ("tiny-qwen2-28h", _lib.BF16, 2e-2),
              ("tiny-qwen2-g7", _lib.BF16, 2e-2), ("tiny-phi2", _lib.BF16, 2e-2), ("tiny-phi3", _lib.BF16, 2e-2),
              ("tiny-gemma", _lib.BF16, 2e-2)]
+    # the benchmark's own shard shapes: full-width qwen2-7b (at 8 ranks: 4 query heads per rank with a padded head,
+    # a KV head shared by a rank pair, 2368 intermediate units) and phi2, cut to two layers so that the CPU oracle
+    # finishes in seconds
+    if os.environ.get("TP_CHECK_FULL", "1") == "1":
+        cases += [("qwen2-7b", _lib.BF16, 2e-2), ("phi2", _lib.BF16, 2e-2)]
     only = os.environ.get("TP_CHECK_ONLY")          # debugging: comma-separated configuration names
     prompts = [int(x) for x in os.environ.get("TP_CHECK_PROMPTS", "40,150").split(",")]
     for name, dtype, tol in cases:
         if only and name not in only.split(","):
             continue
         cfg = configs.get(name)
+        full_width = name in configs.BASELINE
+        if full_width:
+            cfg["num_hidden_layers"] = 2
         nkv = cfg.get("num_key_value_heads") or cfg["num_attention_heads"]
         if not ((world <= nkv and nkv % world == 0) or (world > nkv and world % nkv == 0)):
             continue
@@ -53,7 +61,7 @@ def main():
         m.update_params(w)
         # 80 prompt rows go through the peer-memory exchange, 300 rows through NCCL; decode steps
         # (2 rows) always through the exchange
-        for plen in prompts:
+        for plen in (prompts[:1] if full_width else prompts):
             prompt = synth.prompt(cfg, 2, plen, 31)
             want = ref = None
             if rank == 0:
