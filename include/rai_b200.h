@@ -315,6 +315,10 @@ int32_t rb_model_destroy(rb_model* m);
  * types Tensor::from_safetensor accepts, rai-core/src/hlops/from_safetensor.rs:51-91). */
 int32_t rb_model_load_param(rb_model* m, const char* name, const void* data, int32_t on_device, int32_t src_dtype,
                             int32_t rank, const int64_t* shape);
+/* The way back, for Module::to_safetensors / named_params (rai-core/src/nn.rs:31-37,57-75): copies one named
+ * parameter to the host in the MODEL dtype and the parameter's full shape (dst_bytes must be exactly that).  A
+ * tensor-parallel rank returns the rectangle it keeps and zeros elsewhere.  Synchronises the stream. */
+int32_t rb_model_read_param(rb_model* m, const char* name, void* dst_host, size_t dst_bytes);
 /* Module::update_by_safetensors, rai-core/src/nn.rs:39-55: every parameter of the model is looked up by
  * name in the given files (names absent from the model are ignored; a later file wins over an earlier
  * one, like the reference's map insert) and cast to the model dtype; a parameter found in no file fails

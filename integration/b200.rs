@@ -145,6 +145,7 @@ extern "C" {
     pub fn rb_model_create(ctx: *mut rb_ctx, cfg: *const rb_model_config, out: *mut *mut rb_model) -> i32;
     pub fn rb_model_destroy(m: *mut rb_model) -> i32;
     pub fn rb_model_load_param(m: *mut rb_model, name: *const c_char, data: *const c_void, on_device: i32, src_dtype: i32, rank: i32, shape: *const i64) -> i32;
+    pub fn rb_model_read_param(m: *mut rb_model, name: *const c_char, dst_host: *mut c_void, dst_bytes: usize) -> i32;
     pub fn rb_model_load_safetensors(m: *mut rb_model, paths: *const *const c_char, n_paths: i32) -> i32;
     pub fn rb_safetensors_open(path: *const c_char, out: *mut *mut rb_safetensors) -> i32;
     pub fn rb_safetensors_close(st: *mut rb_safetensors) -> i32;

@@ -25,7 +25,7 @@ namespace rb {
 
 using bf16 = __nv_bfloat16;
 
-int attention_decode_splits(rb_ctx* ctx, int batch, int kv_heads, int max_len);
+int attention_decode_splits(rb_ctx* ctx, int batch, int kv_heads, int max_len, int head_dim);
 
 // Split-KV scratch of the context, grow-only.  A captured decode step has the buffer's address baked in, and other
 // models or direct calls on the same context may need more later: a buffer that has been handed out is therefore
@@ -601,7 +601,7 @@ int launch_attention(rb_ctx* ctx, rb_kv_cache* c, AParams& p, int batch, int max
   }
   // Split the keys of a sequence over several blocks only when (sequence, KV head) pairs alone leave
   // the GPU under-filled: one long block per pair keeps its copy pipeline full and needs no merge.
-  const int splits = attention_decode_splits(ctx, batch, p.kv_heads, max_len);
+  const int splits = attention_decode_splits(ctx, batch, p.kv_heads, max_len, D);
   p.n_splits = splits;
   if (splits > 1) {
     RB_TRY(attention_reserve_scratch(ctx, (size_t)batch * p.q_heads * splits * (D + 2) * sizeof(float)));
@@ -642,7 +642,7 @@ static std::mutex g_static_attn_scratch_lock;
 
 template <int D>
 static int launch_attention_decode_static(rb_ctx* ctx, rb_kv_cache* c, AParams& p, int batch, int max_len, float* scratch) {
-  const int splits = attention_decode_splits(ctx, batch, p.kv_heads, max_len);
+  const int splits = attention_decode_splits(ctx, batch, p.kv_heads, max_len, D);
   p.n_splits = splits;
   if (splits > 1) {
     const size_t need = (size_t)batch * p.q_heads * splits * (D + 2);
@@ -664,14 +664,14 @@ static int launch_attention_decode_static(rb_ctx* ctx, rb_kv_cache* c, AParams& 
   return RB_OK;
 }
 
-int attention_decode_splits(rb_ctx* ctx, int batch, int kv_heads, int max_len) {
+int attention_decode_splits(rb_ctx* ctx, int batch, int kv_heads, int max_len, int head_dim) {
   // One block per (sequence, KV head) keeps its copy pipeline full and needs no merge; splitting the
   // keys only pays when those pairs under-fill the GPU.  Cost model in units of key tiles: a launch
   // runs ceil(blocks / resident blocks) waves, each as long as one block's tiles plus a fixed start-up,
   // and a split launch pays for the merge kernel.
   const int tiles = std::max(1, (max_len + kTile - 1) / kTile);
   const int work = batch * kv_heads;
-  const int slots = 2 * ctx->sm_count;
+  const int slots = (head_dim <= 128 ? 2 : 1) * ctx->sm_count;  // blocks resident at once (head size 256: one per SM)
   int best = 1;
   double best_cost = 1e30;
   for (int s = 1; s <= std::min(tiles, 32); ++s) {

@@ -140,7 +140,7 @@ bool attention_can_fuse_rope(const rb_kv_cache* c, int q_heads, int rot, const v
 int attention_decode_fused_rope(rb_ctx* ctx, const void* qkv, const float* acc, int n_acc, const void* bias,
                                 const float* cos_t, const float* sin_t, int rot, rb_kv_cache* c, int layer, int batch,
                                 int q_heads, float scale, void* out);
-int attention_decode_splits(rb_ctx* ctx, int batch, int kv_heads, int max_len);
+int attention_decode_splits(rb_ctx* ctx, int batch, int kv_heads, int max_len, int head_dim);
 int attention_reserve_scratch(rb_ctx* ctx, size_t bytes);
 int attention_simple(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, int batch, int s_new, int q_heads,
                      float scale, void* out, int dtype);

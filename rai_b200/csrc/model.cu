@@ -378,6 +378,8 @@ int forward_impl(rb_model* m, const uint32_t* tokens, int batch, int seq, int po
 int forward_body(rb_model* m, const uint32_t* tokens, int batch, int seq, void* logits_out, const int32_t* last_rows) {
   const rb_model_config& c = m->cfg;
   rb_ctx* ctx = m->ctx;
+  RB_REQUIRE(c.tp_size == 1 || m->comm || m->shard_only,
+             "forward: this is rank %d of a %d-way tensor-parallel model and rb_model_tp_init has not run", c.tp_rank, c.tp_size);
   const int64_t rows = (int64_t)batch * seq;
   const int H = c.hidden_size, d = m->d;
 
@@ -983,6 +985,25 @@ extern "C" int32_t rb_model_load_safetensors(rb_model* m, const char* const* pat
   return rb_model_finalize(m);
 }
 
+extern "C" int32_t rb_model_read_param(rb_model* m, const char* name, void* dst_host, size_t dst_bytes) {
+  RB_REQUIRE(m && name && dst_host, "rb_model_read_param: null argument");
+  auto it = m->params.find(name);
+  if (it == m->params.end()) return fail(RB_ERR_PARAM, "parameter '%s' is not part of this model", name);
+  const ParamSpec& sp = it->second;
+  const size_t row_bytes = (size_t)sp.cols * m->es, need = (size_t)sp.rows * row_bytes;
+  RB_REQUIRE(dst_bytes == need, "rb_model_read_param: '%s' is %zu bytes in the model dtype, the buffer holds %zu", name, need,
+             dst_bytes);
+  RB_CUDA(cudaStreamSynchronize(m->ctx->stream));
+  memset(dst_host, 0, need);  // what a tensor-parallel rank does not keep reads as zero
+  for (const Piece& pc : sp.pieces) {
+    if (pc.rows == 0 || pc.cols == 0) continue;
+    char* dst = (char*)dst_host + (size_t)pc.src_row0 * row_bytes + (size_t)pc.src_col0 * m->es;
+    RB_CUDA(cudaMemcpy2D(dst, row_bytes, pc.dst, (size_t)pc.dst_ld * m->es, (size_t)pc.cols * m->es, (size_t)pc.rows,
+                         cudaMemcpyDeviceToHost));
+  }
+  return RB_OK;
+}
+
 extern "C" int32_t rb_model_finalize(rb_model* m) {
   RB_REQUIRE(m, "rb_model_finalize: null model");
   for (const std::string& n : m->names)
@@ -1107,7 +1128,7 @@ int sample_tokens(rb_model* m, int batch, uint32_t* out) {
 int decode_plan(rb_model* m, int batch) {
   int max_len = 0;
   for (int b = 0; b < batch; ++b) max_len = std::max(max_len, m->cache->host_lens[b]);
-  return attention_decode_splits(m->ctx, batch, m->nkv_l, max_len);
+  return attention_decode_splits(m->ctx, batch, m->nkv_l, max_len, m->d);
 }
 
 int decode_step_launches(rb_model* m, int batch) {

@@ -217,6 +217,24 @@ class Model:
                   ctypes.c_void_p(v.data_ptr()))
         return k.float(), v.float()
 
+    def read_param(self, name: str) -> torch.Tensor:
+        """One named parameter back on the host, in the model dtype and the parameter's full shape (a tensor-parallel
+        rank returns the rectangle it keeps, zeros elsewhere)."""
+        from . import synth
+        shapes = {n: sh for n, sh, _ in synth.param_shapes(self.cfg)}
+        t = torch.empty(shapes[name], dtype=_TORCH_DTYPE[self.dtype])
+        _lib.call("rb_model_read_param", self._m, name.encode(), ctypes.c_void_p(t.data_ptr()), t.numel() * t.element_size())
+        return t
+
+    def to_safetensors(self, path: str) -> None:
+        """Module::to_safetensors (rai-core/src/nn.rs:31-37): every named parameter, in the model dtype."""
+        from . import safetensors_io
+        named = {n: self.read_param(n) for n in self.param_names()}
+        if self.dtype == _lib.BF16:
+            safetensors_io.write_safetensors(path, {k: v.float().numpy() for k, v in named.items()}, "BF16")
+        else:
+            safetensors_io.write_safetensors(path, {k: v.numpy() for k, v in named.items()}, "F32")
+
     def param_bytes(self) -> int:
         return int(_lib.lib().rb_model_param_bytes(self._m))
 

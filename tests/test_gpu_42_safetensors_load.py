@@ -111,21 +111,49 @@ def test_missing_and_misshapen_parameters_fail_by_name(cuda, tmp_path):
 
 @pytest.mark.parametrize("name,tp,rank", [("tiny-qwen2", 2, 1), ("tiny-qwen2-28h", 8, 5), ("tiny-phi2", 2, 0)])
 def test_tensor_parallel_rank_keeps_the_same_shard(cuda, tmp_path, name, tp, rank):
-    """One rank's shard without its peers (its own kernels only): the shard built from the files, where only
-    the rows the rank keeps are uploaded, must equal the shard built from whole tensors."""
+    """One rank's shard, read back parameter by parameter: the shard built from the files, where only the rows the
+    rank keeps are uploaded, must equal the shard built from whole tensors, and both must be the rectangle the shard
+    plan names (zeros elsewhere).  A forward pass of a rank without its group is refused, not attempted."""
+    from rai_b200 import tp as tp_plan
     cfg = configs.get(name)
     w = synth.weights(cfg, 16)
     p = str(tmp_path / "model.safetensors")
     write_safetensors(p, w, "BF16")
     rounded = {k: torch.from_numpy(v).to(torch.bfloat16).float().numpy() for k, v in w.items()}
-    old = os.environ.get("RAI_B200_SHARD_ONLY")
-    os.environ["RAI_B200_SHARD_ONLY"] = "1"
-    try:
-        got = _from_files(cuda, cfg, _lib.BF16, [p], tp_rank=rank, tp_size=tp)
-        want = _by_name(cuda, cfg, _lib.BF16, rounded, tp_rank=rank, tp_size=tp)
-    finally:
-        if old is None:
-            os.environ.pop("RAI_B200_SHARD_ONLY", None)
-        else:
-            os.environ["RAI_B200_SHARD_ONLY"] = old
-    assert torch.isfinite(got).all() and torch.equal(got, want)
+    a = Model(cfg, _lib.BF16, cuda, 2, 64, 32, tp_rank=rank, tp_size=tp)
+    a.update_by_safetensors([p])
+    b = Model(cfg, _lib.BF16, cuda, 2, 64, 32, tp_rank=rank, tp_size=tp)
+    b.update_params(rounded)
+    kept_any = False
+    for n in a.param_names():
+        ta, tb = a.read_param(n), b.read_param(n)
+        assert torch.equal(ta, tb), n
+        full = torch.from_numpy(rounded[n]).to(torch.bfloat16)
+        nz = ta != 0
+        assert torch.equal(ta[nz], full[nz]), n      # what the rank keeps is the checkpoint's values
+        kept_any = kept_any or bool(nz.any())
+    assert kept_any
+    if cfg["arch"] != "phi2":
+        plan = tp_plan.plan(cfg, rank, tp)
+        got = a.read_param("model.layers.0.mlp.gate_proj.weight")
+        want = torch.zeros_like(got)
+        want[plan.inter] = torch.from_numpy(rounded["model.layers.0.mlp.gate_proj.weight"]).to(torch.bfloat16)[plan.inter]
+        assert torch.equal(got, want)
+    with pytest.raises(_lib.RaiB200Error, match="rb_model_tp_init"):
+        a.forward(synth.prompt(cfg, 2, 4, 3), 0)
+    a.close()
+    b.close()
+
+
+def test_parameters_round_trip_through_to_safetensors(cuda, tmp_path):
+    """Module::to_safetensors then update_by_safetensors gives the same model (rai-core/src/nn.rs:31-55)."""
+    cfg = configs.get("tiny-qwen2")
+    w = synth.weights(cfg, 23)
+    m = Model(cfg, _lib.BF16, cuda, 2, 64, 32)
+    m.update_params(w)
+    first = _logits(m, cfg)
+    path = str(tmp_path / "saved.safetensors")
+    m.to_safetensors(path)
+    m.close()
+    again = _from_files(cuda, cfg, _lib.BF16, [path])
+    assert torch.equal(first, again)
