@@ -83,6 +83,7 @@ extern "C" int32_t rb_init(int32_t device, rb_ctx** out) {
   c->debug_no_fuse = nf && nf[0] == '0';
   const char* pdl = getenv("RAI_B200_PDL");
   c->pdl = !(pdl && pdl[0] == '0');
+  if (const char* at = getenv("RAI_B200_ATTN_TC")) c->attn_tc = at[0] != '0';
   if (const char* gr = getenv("RAI_B200_GEMM_REDUCE")) c->gemm_reduce = gr[0] != '0';
   if (const char* rk = getenv("RAI_B200_GEMM_RING_KB")) {
     const long kb = atol(rk);

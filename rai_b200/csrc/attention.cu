@@ -705,6 +705,9 @@ int attention_mma_bf16(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, in
   p.wait_cycles = ctx->wait_budget_cycles;
   RB_REQUIRE(p.group >= 1 && p.group <= 16 && q_heads % c->kv_heads == 0,
              "attention: %d query heads per KV head unsupported (1..16)", p.group);
+  // prefill with at least one 128-row query tile and head size 64 or 128: the tcgen05 kernel
+  if (ctx->attn_tc && attention_prefill_tc_supported(c, s_new, q_heads, q, out))
+    return attention_prefill_tc(ctx, q, c, layer, batch, s_new, q_heads, scale, out);
   int max_len = 0;
   for (int b = 0; b < batch; ++b) max_len = std::max(max_len, c->host_lens[b]);
   switch (c->head_dim) {

@@ -21,6 +21,7 @@ struct rb_ctx {
   bool pdl = true;            // RAI_B200_PDL=0 turns programmatic dependent launch off (debugging aid)
   // shared memory a decode-sized GEMM spends on its operand ring (RAI_B200_GEMM_RING_KB overrides)
   size_t gemm_ring_bytes = 200 * 1024;
+  bool attn_tc = true;        // RAI_B200_ATTN_TC=0: prefill attention on the mma.sync kernel for every head size (debugging aid)
   bool gemm_reduce = true;    // RAI_B200_GEMM_REDUCE=0: tensor-parallel GEMMs leave split-K to separate kernels (debugging aid)
   float* gemm_scratch = nullptr;   // float32 slabs of the GEMMs that reduce split-K inside the kernel; grow-only
   size_t gemm_scratch_bytes = 0;
@@ -142,6 +143,10 @@ int attention_decode_fused_rope(rb_ctx* ctx, const void* qkv, const float* acc, 
                                 int q_heads, float scale, void* out);
 int attention_decode_splits(rb_ctx* ctx, int batch, int kv_heads, int max_len, int head_dim);
 int attention_reserve_scratch(rb_ctx* ctx, size_t bytes);
+// attention_tc.cu: causal prefill attention on tcgen05 (head sizes 64 and 128, query length >= 128)
+bool attention_prefill_tc_supported(const rb_kv_cache* c, int s_new, int q_heads, const void* q, const void* out);
+int attention_prefill_tc(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, int batch, int s_new, int q_heads, float scale,
+                         void* out);
 int attention_simple(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, int batch, int s_new, int q_heads,
                      float scale, void* out, int dtype);
 }  // namespace rb
