@@ -213,34 +213,39 @@ def decode_timeline(model, dev, rewind, first, T0, path=None, steps=4):
     """Kernel start/end times of `steps` decode steps as the device ran them (graph replay, dependent launches
     overlapping), from the CUDA activity records torch's profiler collects.  With dependent launches a kernel's own
     duration includes the time it sits waiting for its predecessor, so the figure kept per kernel name is its
-    `advance`: how far it moves the end of the step (its end minus the latest end before it).  Returns the summary
-    (None when no activity records are available) and writes it, with the raw sequence of one step, to `path`."""
+    `advance`: how far it moves the end of the step (its end minus the latest end before it).  One more step is
+    traced than is kept: the first traced step starts from an idle device (its first kernel's advance would include the
+    profiler's own start-up gap) and is dropped.  Returns the summary (None when no activity records are available) and
+    writes it, with the raw sequence of one step, to `path`."""
     import torch
     from torch.profiler import ProfilerActivity, profile
     rewind(T0)
     model.decode_loop(first, T0, 2)
     dev.synchronize()
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
-        model.decode_loop(first, T0 + 2, steps)
+        model.decode_loop(first, T0 + 2, steps + 1)
         dev.synchronize()
     evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and e.time_range.end > e.time_range.start]
     evs.sort(key=lambda e: e.time_range.start)
     if not evs:
         return None
     t0 = evs[0].time_range.start
-    seq, by_name, prev_end = [], {}, None
+    seq, prev_end = [], None
     for e in evs:
         name = e.name.replace("(anonymous namespace)::", "").replace("void ", "").replace("rb::", "").split("(")[0]
         start, end = e.time_range.start - t0, e.time_range.end - t0
         advance = (end - start) if prev_end is None else max(0.0, end - prev_end)
         prev_end = end if prev_end is None else max(prev_end, end)
         seq.append({"name": name, "start_us": round(start, 2), "dur_us": round(end - start, 2), "advance_us": round(advance, 2)})
-        a = by_name.setdefault(name, {"launches": 0, "advance_us": 0.0})
+    n = len(seq) // (steps + 1)
+    kept = seq[n:]                      # drop the first traced step
+    by_name = {}
+    for x in kept:
+        a = by_name.setdefault(x["name"], {"launches": 0, "advance_us": 0.0})
         a["launches"] += 1
-        a["advance_us"] += advance
-    span = max(x["start_us"] + x["dur_us"] for x in seq)
+        a["advance_us"] += x["advance_us"]
+    span = (max(x["start_us"] + x["dur_us"] for x in kept) - max(x["start_us"] + x["dur_us"] for x in seq[:n])) if n else 0.0
     per_step = {k: {kk: round(vv / steps, 2) for kk, vv in v.items()} for k, v in by_name.items()}
-    n = len(seq) // steps
     out = {"steps": steps, "span_us_per_step": round(span / steps, 1), "per_kernel_per_step": per_step}
     if path:
         json.dump(dict(out, one_step=seq[n:2 * n]), open(path, "w"), indent=1)

@@ -61,8 +61,9 @@ enum { RB_ARCH_QWEN2 = 0, RB_ARCH_PHI2 = 1, RB_ARCH_PHI3 = 2, RB_ARCH_GEMMA = 3 
 enum {
   RB_UN_NEG = 0, RB_UN_EXP, RB_UN_SQRT, RB_UN_RSQRT, RB_UN_SQUARE, RB_UN_TANH, RB_UN_ERF, RB_UN_SIN,
   RB_UN_COS, RB_UN_POWF, RB_UN_SILU, RB_UN_GELU_TANH, RB_UN_GELU_ERF, RB_UN_RELU, RB_UN_LOG, RB_UN_ABS,
-  RB_UN_RECIP, RB_UN_ADD_SCALAR, RB_UN_MUL_SCALAR
+  RB_UN_RECIP, RB_UN_ADD_SCALAR, RB_UN_MUL_SCALAR, RB_UN_SIGN, RB_UN_LOG2, RB_UN_LOG10
 };
+enum { RB_CMP_EQ = 0, RB_CMP_NE, RB_CMP_GT, RB_CMP_GE, RB_CMP_LT, RB_CMP_LE };
 enum { RB_BIN_ADD = 0, RB_BIN_SUB, RB_BIN_MUL, RB_BIN_DIV, RB_BIN_MAXIMUM, RB_BIN_MINIMUM };
 enum { RB_RED_SUM = 0, RB_RED_MAX, RB_RED_MIN };
 
@@ -274,6 +275,40 @@ int32_t rb_arange(rb_ctx* ctx, void* out_dev, int64_t n, double start, double st
  * batch stride 0 = broadcast; trans_b != 0 means B[b] is stored [n,k] (the `.t()` of Linear). */
 int32_t rb_matmul(rb_ctx* ctx, const void* a_dev, const void* b_dev, void* c_dev, int64_t batch, int64_t m, int64_t n,
                   int64_t k, int64_t a_batch_stride, int64_t b_batch_stride, int32_t trans_b, int32_t dtype);
+
+/* ---- the rest of the rule set of rai-core/src/dispatch.rs:41-157, for graphs beyond the decoders (vision models,
+ * training examples).  Correctness-first kernels: one thread per output element. ---- */
+/* Equal / NotEqual / Greater / GreaterEqual / Less / LessEqual (candle.rs:327-399): u8 result; operands as rb_binary. */
+int32_t rb_compare(rb_ctx* ctx, int32_t op, const void* a_dev, const int64_t* a_strides, const void* b_dev,
+                   const int64_t* b_strides, uint8_t* out_dev, int32_t rank, const int64_t* shape, int32_t dtype);
+/* LogSoftmax over the last dimension of [rows, cols] (candle.rs:805-836). */
+int32_t rb_log_softmax_rows(rb_ctx* ctx, const void* x_dev, void* out_dev, int64_t rows, int64_t cols, int32_t dtype);
+/* ArgMin over the last dimension (candle.rs:933-945 family): first index among equal minima. */
+int32_t rb_argmin_rows(rb_ctx* ctx, const void* x_dev, int32_t dtype, int64_t rows, int64_t cols, uint32_t* out_dev);
+/* ScatterAdd (candle.rs:990-1004; inputs x, updates, indices) and, with index_is_1d != 0, IndexAdd (candle.rs:851-865;
+ * inputs x, source, index): tensors viewed as [outer, dim, inner]; out = x, then out[o, idx, i] += src[o, j, i] with
+ * idx = index[o, j, i] (or index[j]).  out may be x itself.  An index beyond dim_out is skipped and reported. */
+int32_t rb_scatter_add(rb_ctx* ctx, const void* x_dev, const void* src_dev, const uint32_t* idx_dev, void* out_dev,
+                       int64_t outer, int64_t dim_out, int64_t dim_src, int64_t inner, int32_t index_is_1d, int32_t dtype);
+/* Conv2d (candle.rs:628-663; ops/conv2d.rs:5-9) on NCHW input [N, Cin, H, W] and weight [Cout, Cin, KH, KW]; Conv1d
+ * (ops/conv1d.rs:5-9) is the H = KH = 1 case.  out_shape4 (optional) receives [N, Cout, OH, OW]; with out_dev == NULL
+ * the call only reports the shape. */
+int32_t rb_conv2d(rb_ctx* ctx, const void* x_dev, const int32_t* x_shape4, const void* w_dev, const int32_t* w_shape4,
+                  const int32_t* padding2, const int32_t* stride2, const int32_t* dilation2, void* out_dev,
+                  int32_t* out_shape4, int32_t dtype);
+/* ConvTranspose2d / 1d (candle.rs:702-760; ops/conv_transpose2d.rs:5-10): weight [Cin, Cout, KH, KW]. */
+int32_t rb_conv_transpose2d(rb_ctx* ctx, const void* x_dev, const int32_t* x_shape4, const void* w_dev,
+                            const int32_t* w_shape4, const int32_t* padding2, const int32_t* out_padding2,
+                            const int32_t* stride2, const int32_t* dilation2, void* out_dev, int32_t* out_shape4,
+                            int32_t dtype);
+/* MaxPool2d / AvgPool2d and their 1-D forms (ops/max_pool2d.rs:6-11, ops/avg_pool2d.rs:9-13): is_max != 0 takes the
+ * maximum over the part of the window inside the input, else the sum over it divided by the full window size. */
+int32_t rb_pool2d(rb_ctx* ctx, int32_t is_max, const void* x_dev, const int32_t* x_shape4, const int32_t* kernel2,
+                  const int32_t* stride2, const int32_t* padding2, const int32_t* dilation2, void* out_dev,
+                  int32_t* out_shape4, int32_t dtype);
+/* UpsampleNearest2d / 1d (ops/upsample_nearest2d.rs:6-8): [N, C, H, W] -> [N, C, out_h, out_w]. */
+int32_t rb_upsample_nearest2d(rb_ctx* ctx, const void* x_dev, const int32_t* x_shape4, int32_t out_h, int32_t out_w,
+                              void* out_dev, int32_t dtype);
 
 /* ======================================================================================
  * Decoder driver — Model::new / Module::update_by_safetensors / Model::fwd / clear_kv_cache of

@@ -142,6 +142,14 @@ extern "C" {
     pub fn rb_fill(ctx: *mut rb_ctx, out_dev: *mut c_void, n: i64, value: f64, dtype: i32) -> i32;
     pub fn rb_arange(ctx: *mut rb_ctx, out_dev: *mut c_void, n: i64, start: f64, step: f64, dtype: i32) -> i32;
     pub fn rb_matmul(ctx: *mut rb_ctx, a_dev: *const c_void, b_dev: *const c_void, c_dev: *mut c_void, batch: i64, m: i64, n: i64, k: i64, a_batch_stride: i64, b_batch_stride: i64, trans_b: i32, dtype: i32) -> i32;
+    pub fn rb_compare(ctx: *mut rb_ctx, op: i32, a_dev: *const c_void, a_strides: *const i64, b_dev: *const c_void, b_strides: *const i64, out_dev: *mut u8, rank: i32, shape: *const i64, dtype: i32) -> i32;
+    pub fn rb_log_softmax_rows(ctx: *mut rb_ctx, x_dev: *const c_void, out_dev: *mut c_void, rows: i64, cols: i64, dtype: i32) -> i32;
+    pub fn rb_argmin_rows(ctx: *mut rb_ctx, x_dev: *const c_void, dtype: i32, rows: i64, cols: i64, out_dev: *mut u32) -> i32;
+    pub fn rb_scatter_add(ctx: *mut rb_ctx, x_dev: *const c_void, src_dev: *const c_void, idx_dev: *const u32, out_dev: *mut c_void, outer: i64, dim_out: i64, dim_src: i64, inner: i64, index_is_1d: i32, dtype: i32) -> i32;
+    pub fn rb_conv2d(ctx: *mut rb_ctx, x_dev: *const c_void, x_shape4: *const i32, w_dev: *const c_void, w_shape4: *const i32, padding2: *const i32, stride2: *const i32, dilation2: *const i32, out_dev: *mut c_void, out_shape4: *mut i32, dtype: i32) -> i32;
+    pub fn rb_conv_transpose2d(ctx: *mut rb_ctx, x_dev: *const c_void, x_shape4: *const i32, w_dev: *const c_void, w_shape4: *const i32, padding2: *const i32, out_padding2: *const i32, stride2: *const i32, dilation2: *const i32, out_dev: *mut c_void, out_shape4: *mut i32, dtype: i32) -> i32;
+    pub fn rb_pool2d(ctx: *mut rb_ctx, is_max: i32, x_dev: *const c_void, x_shape4: *const i32, kernel2: *const i32, stride2: *const i32, padding2: *const i32, dilation2: *const i32, out_dev: *mut c_void, out_shape4: *mut i32, dtype: i32) -> i32;
+    pub fn rb_upsample_nearest2d(ctx: *mut rb_ctx, x_dev: *const c_void, x_shape4: *const i32, out_h: i32, out_w: i32, out_dev: *mut c_void, dtype: i32) -> i32;
     pub fn rb_model_create(ctx: *mut rb_ctx, cfg: *const rb_model_config, out: *mut *mut rb_model) -> i32;
     pub fn rb_model_destroy(m: *mut rb_model) -> i32;
     pub fn rb_model_load_param(m: *mut rb_model, name: *const c_char, data: *const c_void, on_device: i32, src_dtype: i32, rank: i32, shape: *const i64) -> i32;

@@ -24,7 +24,8 @@ ACT_NONE, ACT_SILU, ACT_GELU_TANH, ACT_GELU_ERF, ACT_RELU = range(5)
 NORM_RMS, NORM_RMS_ONE_PLUS, NORM_LAYER = range(3)
 ARCH_QWEN2, ARCH_PHI2, ARCH_PHI3, ARCH_GEMMA = range(4)
 (UN_NEG, UN_EXP, UN_SQRT, UN_RSQRT, UN_SQUARE, UN_TANH, UN_ERF, UN_SIN, UN_COS, UN_POWF, UN_SILU, UN_GELU_TANH,
- UN_GELU_ERF, UN_RELU, UN_LOG, UN_ABS, UN_RECIP, UN_ADD_SCALAR, UN_MUL_SCALAR) = range(19)
+ UN_GELU_ERF, UN_RELU, UN_LOG, UN_ABS, UN_RECIP, UN_ADD_SCALAR, UN_MUL_SCALAR, UN_SIGN, UN_LOG2, UN_LOG10) = range(22)
+CMP_EQ, CMP_NE, CMP_GT, CMP_GE, CMP_LT, CMP_LE = range(6)
 BIN_ADD, BIN_SUB, BIN_MUL, BIN_DIV, BIN_MAXIMUM, BIN_MINIMUM = range(6)
 RED_SUM, RED_MAX, RED_MIN = range(3)
 
@@ -48,7 +49,7 @@ class ModelConfig(ctypes.Structure):
 
 
 _SCALARS = {"int32_t": ctypes.c_int32, "int64_t": ctypes.c_int64, "size_t": ctypes.c_size_t, "float": ctypes.c_float,
-            "double": ctypes.c_double, "uint32_t": ctypes.c_uint32}
+            "double": ctypes.c_double, "uint32_t": ctypes.c_uint32, "uint8_t": ctypes.c_uint8}
 
 
 def _ctype_of(decl: str):

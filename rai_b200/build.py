@@ -20,7 +20,7 @@ OBJ = PKG / "csrc" / "build"
 LIB = PKG / "librai_b200.so"
 HEADER = PKG.parent / "include" / "rai_b200.h"
 
-SOURCES = ["api.cu", "decoder_kernels.cu", "plain_kernels.cu", "primitives.cu", "gemm_tc.cu", "attention.cu", "attention_tc.cu", "model.cu", "safetensors.cu", "selftest.cu"]
+SOURCES = ["api.cu", "decoder_kernels.cu", "plain_kernels.cu", "primitives.cu", "primitives_more.cu", "gemm_tc.cu", "attention.cu", "attention_tc.cu", "model.cu", "safetensors.cu", "selftest.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -12,15 +12,18 @@
 //              its [keys][head_dim] tile as an MN-major operand - no transposed copy of V anywhere;
 //   warps 2-5  softmax: each thread owns one query row (its TMEM lane), so row max and row sum need no shuffles.
 //              tcgen05.ld the scores, scale + mask, online softmax in float32, P rounded to bf16 into shared memory in
-//              the swizzled K-major layout the MMA reads.  O stays in tensor memory for the whole walk; when a row's
-//              running max grows, the warp rescales its 32 lanes of O in place (tcgen05.ld / multiply / tcgen05.st),
-//              which after the first few tiles is rare.  At the end O / l goes out as bf16 rows.
+//              the swizzled K-major layout the MMA reads.  O stays in tensor memory for the whole walk; the reference
+//              point of the exponentials follows the running max lazily (it moves only when the max has grown by more
+//              than 2^8), so the in-place rescaling of O (tcgen05.ld / multiply / tcgen05.st) runs a handful of times
+//              per walk.  At the end O / l goes out as bf16 rows.
 // The score MMA of tile j+1 is issued before the P.V MMA of tile j, so the tensor pipe computes the next scores while
 // the softmax warps work on the current ones; two CTAs fit per SM (112 KB of shared memory, 256 TMEM columns
 // each), which overlaps one CTA's softmax with the other's MMAs.
 //
 // Every wait is bounded; a give-up is recorded in the context's status word, in-flight copies are drained, the TMEM
 // allocation is freed and the CTA returns without writing output.
+#include <stdlib.h>
+
 #include <algorithm>
 
 #include "ctx.h"
@@ -51,6 +54,13 @@ struct TCfg {
   static constexpr uint32_t kOCol = 2 * kBN;
 };
 
+// 2^x by the special-function unit (2 ulp; -inf gives +0, which is what a masked score must contribute)
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct TParams {
   const int32_t* block_table;
   const int32_t* seq_lens;
@@ -59,7 +69,16 @@ struct TParams {
   bf16* out;
   uint32_t* status;
   long long wait_cycles;
+#ifdef RB_DEBUG_AIDS
+  unsigned long long* trace;  // developer build: cycles per phase of one softmax thread (see launch_tc)
+#endif
 };
+
+#ifdef RB_DEBUG_AIDS
+#define RB_TICK(slot) do { if (tracing) { const long long _t = clock64(); tr[slot] += (unsigned long long)(_t - t_prev); t_prev = _t; } } while (0)
+#else
+#define RB_TICK(slot) do { } while (0)
+#endif
 
 struct Ctrl {  // lives in dynamic shared memory behind the tiles
   uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, o_done;
@@ -206,6 +225,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     const bool windowed = p.window < (1 << 30);
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
+#ifdef RB_DEBUG_AIDS
+    const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 64;
+    unsigned long long tr[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long t_prev = clock64();
+#endif
     for (int j = 0; j < n; ++j) {
       const int st = j & 1;
       const uint32_t ph = (uint32_t)(j >> 1) & 1u;
@@ -213,6 +237,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
       // the four warps run warp-wide TMEM accesses below: a give-up must be a whole-warp decision
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctl->s_full[st], ph, abort_flag, p.wait_cycles))) { ok = false; break; }
       ptx::tc_fence_after();
+      RB_TICK(0);  // waiting for the scores
       float s[kBN];
       {
         uint32_t r0[32], r1[32];
@@ -225,39 +250,56 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&ctl->s_empty[st]);  // the score buffer may be overwritten
-      // scale, mask (diagonal tiles and windows only), row max
-      float mx = -INFINITY;
-      if (key0 + kBN - 1 > base + q0 || windowed) {
+      RB_TICK(1);  // reading them out of tensor memory
+      // mask (only tiles that the causal diagonal or the window actually cuts), then the row max over the raw scores;
+      // the scale is positive, so it commutes with the max and rides in the exponent's multiply-add below
+      const bool causal_edge = key0 + kBN - 1 > base + q0;
+      const bool window_edge = windowed && key0 + kBN > base && base + q0 + kBM - 1 - p.window > key0;
+      if (causal_edge || window_edge) {
 #pragma unroll
         for (int i = 0; i < kBN; ++i) {
           const int key = key0 + i;
           const bool seen = key <= row_abs && (key < base || key + p.window >= row_abs);
-          s[i] = seen ? s[i] * p.scale_log2 : -INFINITY;
-          mx = fmaxf(mx, s[i]);
+          s[i] = seen ? s[i] : -INFINITY;
         }
-      } else {
-#pragma unroll
-        for (int i = 0; i < kBN; ++i) { s[i] *= p.scale_log2; mx = fmaxf(mx, s[i]); }
       }
-      const float m_new = fmaxf(m_run, mx);
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four independent chains
+#pragma unroll
+      for (int i = 0; i < kBN; i += 4) {
+        mx4[0] = fmaxf(mx4[0], s[i]); mx4[1] = fmaxf(mx4[1], s[i + 1]);
+        mx4[2] = fmaxf(mx4[2], s[i + 2]); mx4[3] = fmaxf(mx4[3], s[i + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+      // The reference point of the exponentials follows the running max lazily: it moves only when the max has grown
+      // by more than 2^kSlack since it was last set.  softmax is invariant to the reference point (numerator and
+      // denominator carry the same factor), the terms stay below 2^kSlack, well inside float32 and bf16 range, and the
+      // rescaling of O below - a read-modify-write of the whole accumulator row - happens a handful of times per
+      // walk instead of at nearly every tile.
+      constexpr float kSlack = 8.0f;
+      const float m_new = (mx > m_run + kSlack || m_run == -INFINITY) ? mx : m_run;
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = exp2f(m_run - m_use);
-      float sum = 0.f;
+      const float corr = ex2_fast(m_run - m_use);
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t packed[kBN / 2];
 #pragma unroll
-      for (int i = 0; i < kBN; i += 2) {
-        const float p0 = exp2f(s[i] - m_use), p1 = exp2f(s[i + 1] - m_use);
-        sum += p0 + p1;
-        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+      for (int i = 0; i < kBN; i += 4) {
+        const float p0 = ex2_fast(fmaf(s[i], p.scale_log2, -m_use)), p1 = ex2_fast(fmaf(s[i + 1], p.scale_log2, -m_use));
+        const float p2 = ex2_fast(fmaf(s[i + 2], p.scale_log2, -m_use)), p3 = ex2_fast(fmaf(s[i + 3], p.scale_log2, -m_use));
+        sum4[0] += p0; sum4[1] += p1; sum4[2] += p2; sum4[3] += p3;
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
+        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h0);
+        packed[(i >> 1) + 1] = *reinterpret_cast<uint32_t*>(&h1);
       }
+      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       l_run = l_run * corr + sum;
+      RB_TICK(2);  // scale, max, exp, sum, pack
       bool rescaled = false;
       if (j > 0) {
         // P.V of the previous tile must be done before P is overwritten or O is touched
         if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctl->o_done, (uint32_t)(j - 1) & 1u, abort_flag, p.wait_cycles))) { ok = false; break; }
         ptx::tc_fence_after();
-        if (__any_sync(0xffffffffu, m_new > m_run)) {   // warp-uniform: the TMEM accesses below are warp-wide
+        RB_TICK(3);  // waiting for the previous P.V
+        if (__any_sync(0xffffffffu, m_new != m_run)) {   // warp-uniform: the TMEM accesses below are warp-wide
           rescaled = true;
 #pragma unroll 1
           for (int c0 = 0; c0 < D; c0 += 32) {
@@ -270,6 +312,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
           }
         }
       }
+      RB_TICK(4);  // rescaling O
       // P row -> shared memory, K-major with the 128-byte swizzle (16-byte chunk c of row r sits at c ^ (r & 7))
       uint8_t* prow = p_s + row * 128;
 #pragma unroll
@@ -282,7 +325,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&ctl->p_full);
       m_run = m_new;
+      RB_TICK(5);  // storing P, fences, hand-over
     }
+#ifdef RB_DEBUG_AIDS
+    if (tracing) { for (int i = 0; i < 6; ++i) p.trace[i] = tr[i]; p.trace[6] = (unsigned long long)n; }
+#endif
     if (ok) ok = __all_sync(0xffffffffu, ptx::mbar_wait(&ctl->o_done, (uint32_t)(n - 1) & 1u, abort_flag, p.wait_cycles));
     if (ok) {
       ptx::tc_fence_after();
@@ -360,6 +407,28 @@ int launch_tc(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, int batch, 
   p.status = ctx->status_dev;
   p.wait_cycles = ctx->wait_budget_cycles;
   dim3 grid((unsigned)((s_new + kBM - 1) / kBM), (unsigned)q_heads, (unsigned)batch);
+#ifdef RB_DEBUG_AIDS
+  static const bool trace = getenv("RAI_B200_ATTN_TRACE") != nullptr;
+  static int traced = 0;
+  if (trace && traced < 3 && layer == 0) {  // developer build: synchronous, prints where one softmax thread's cycles went
+    ++traced;
+    unsigned long long* tr = nullptr;
+    RB_CUDA(cudaMalloc(&tr, 8 * sizeof(unsigned long long)));
+    RB_CUDA(cudaMemset(tr, 0, 8 * sizeof(unsigned long long)));
+    p.trace = tr;
+    RB_CUDA(launch_kernel(kern, grid, dim3(kThreads), (size_t)C::kSmemBytes, ctx->stream, false, tq, tk, tv, p));
+    RB_CUDA(cudaStreamSynchronize(ctx->stream));
+    unsigned long long h[8];
+    RB_CUDA(cudaMemcpy(h, tr, sizeof(h), cudaMemcpyDeviceToHost));
+    cudaFree(tr);
+    const double nt = h[6] ? (double)h[6] : 1.0;
+    fprintf(stderr, "attention_prefill_tc<%d> s_new=%d tiles=%llu | cycles per tile: wait-scores %.0f  tmem-ld %.0f  softmax-math %.0f  "
+            "wait-prev-PV %.0f  rescale-O %.0f  store-P+handover %.0f\n", D, s_new, h[6], h[0] / nt, h[1] / nt, h[2] / nt, h[3] / nt,
+            h[4] / nt, h[5] / nt);
+    ctx->launches++;
+    return RB_OK;
+  }
+#endif
   RB_CUDA(launch_kernel(kern, grid, dim3(kThreads), (size_t)C::kSmemBytes, ctx->stream, ctx->pdl, tq, tk, tv, p));
   ctx->launches++;
   return RB_OK;

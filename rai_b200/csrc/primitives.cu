@@ -33,6 +33,9 @@ __global__ void unary_kernel(int op, const T* __restrict__ x, T* __restrict__ ou
       case RB_UN_RECIP: y = 1.0f / v; break;
       case RB_UN_ADD_SCALAR: y = v + sc; break;
       case RB_UN_MUL_SCALAR: y = v * sc; break;
+      case RB_UN_SIGN: y = (v > 0.f) ? 1.f : (v < 0.f ? -1.f : 0.f); break;
+      case RB_UN_LOG2: y = log2f(v); break;
+      case RB_UN_LOG10: y = log10f(v); break;
       default: y = v;
     }
     out[i] = Cvt<T>::from_f(y);
@@ -239,7 +242,7 @@ using namespace rb;
 
 extern "C" int32_t rb_unary(rb_ctx* ctx, int32_t op, const void* x, void* out, int64_t n, float scalar, int32_t dtype) {
   RB_REQUIRE(ctx && (n == 0 || (x && out)) && n >= 0, "rb_unary: bad argument");
-  RB_REQUIRE(op >= RB_UN_NEG && op <= RB_UN_MUL_SCALAR, "rb_unary: unknown op %d", op);
+  RB_REQUIRE(op >= RB_UN_NEG && op <= RB_UN_LOG10, "rb_unary: unknown op %d", op);
   if (n == 0) return RB_OK;
   RB_DISPATCH_FLOAT(dtype, "rb_unary", (unary_kernel<T><<<grid_for(n), 256, 0, ctx->stream>>>(op, (const T*)x, (T*)out, n, scalar)));
   ctx->launches++;

@@ -249,6 +249,67 @@ class Tensor:
         m = self.mean(dim, True)
         return (self - m).square().sum(dim, keep_dim) / float(self.size(dim))
 
+    # the rest of the rule set (dispatch.rs:41-157): what graphs beyond the decoders use
+    def minimum(self, o): return self._bin("Minimum", o)
+    def log(self): return self._un("Log")
+    def log2(self): return self._un("Log2")
+    def log10(self): return self._un("Log10")
+    def abs(self): return self._un("Abs")
+    def sign(self): return self._un("Sign")
+    def eq(self, o): return eval_rule(self.device, "Equal")(self, o)
+    def ne(self, o): return eval_rule(self.device, "NotEqual")(self, o)
+    def gt(self, o): return eval_rule(self.device, "Greater")(self, o)
+    def ge(self, o): return eval_rule(self.device, "GreaterEqual")(self, o)
+    def lt(self, o): return eval_rule(self.device, "Less")(self, o)
+    def le(self, o): return eval_rule(self.device, "LessEqual")(self, o)
+
+    def min(self, dim=-1, keep_dim: bool = False) -> "Tensor":
+        return eval_rule(self.device, "ReduceMin")(self, dim, keep_dim)
+
+    def log_softmax(self, dim: int = -1) -> "Tensor":
+        return eval_rule(self.device, "LogSoftmax")(self, dim)
+
+    def argmin(self, dim: int = -1) -> "Tensor":
+        return eval_rule(self.device, "ArgMin")(self, dim)
+
+    def scatter_add(self, dim: int, index: "Tensor", source: "Tensor") -> "Tensor":   # ops/scatter_add.rs
+        return eval_rule(self.device, "ScatterAdd")(self, source, index, dim)
+
+    def index_add(self, dim: int, index: "Tensor", source: "Tensor") -> "Tensor":     # ops/index_add.rs
+        return eval_rule(self.device, "IndexAdd")(self, source, index, dim)
+
+    def conv2d(self, w: "Tensor", padding=(0, 0), stride=(1, 1), dilation=(1, 1)) -> "Tensor":   # ops/conv2d.rs
+        return eval_rule(self.device, "Conv2d")(self, w, padding, stride, dilation)
+
+    def conv1d(self, w: "Tensor", padding=0, stride=1, dilation=1) -> "Tensor":                    # ops/conv1d.rs
+        y = self.unsqueeze(2).conv2d(w.unsqueeze(2), (0, padding), (1, stride), (1, dilation))
+        return y.squeeze(2)
+
+    def conv_transpose2d(self, w: "Tensor", padding=(0, 0), out_padding=(0, 0), stride=(1, 1), dilation=(1, 1)) -> "Tensor":
+        return eval_rule(self.device, "ConvTranspose2d")(self, w, padding, out_padding, stride, dilation)
+
+    def conv_transpose1d(self, w: "Tensor", padding=0, out_padding=0, stride=1, dilation=1) -> "Tensor":
+        y = self.unsqueeze(2).conv_transpose2d(w.unsqueeze(2), (0, padding), (0, out_padding), (1, stride), (1, dilation))
+        return y.squeeze(2)
+
+    def max_pool2d(self, kernel, stride=None, padding=(0, 0), dilation=(1, 1)) -> "Tensor":   # ops/max_pool2d.rs
+        return eval_rule(self.device, "MaxPool2d")(self, kernel, stride or kernel, padding, dilation)
+
+    def avg_pool2d(self, kernel, stride=None, padding=(0, 0)) -> "Tensor":                    # ops/avg_pool2d.rs
+        return eval_rule(self.device, "AvgPool2d")(self, kernel, stride or kernel, padding)
+
+    def max_pool1d(self, kernel, stride=None, padding=0, dilation=1) -> "Tensor":
+        return self.unsqueeze(2).max_pool2d((1, kernel), (1, stride or kernel), (0, padding), (1, dilation)).squeeze(2)
+
+    def avg_pool1d(self, kernel, stride=None, padding=0) -> "Tensor":
+        return self.unsqueeze(2).avg_pool2d((1, kernel), (1, stride or kernel), (0, padding)).squeeze(2)
+
+    def upsample_nearest2d(self, size) -> "Tensor":                                            # ops/upsample_nearest2d.rs
+        return eval_rule(self.device, "UpsampleNearest2d")(self, size)
+
+    def upsample_nearest1d(self, size: int) -> "Tensor":
+        return self.unsqueeze(2).upsample_nearest2d((1, size)).squeeze(2)
+
     def index_select(self, dim: int, index: "Tensor") -> "Tensor":
         return eval_rule(self.device, "IndexSelect")(self, dim, index)
 
@@ -285,8 +346,12 @@ def _to_contiguous(x: Tensor) -> Tensor:
 
 _UNARY = {"Negative": _lib.UN_NEG, "Exp": _lib.UN_EXP, "Sqrt": _lib.UN_SQRT, "Rsqrt": _lib.UN_RSQRT, "Square": _lib.UN_SQUARE,
           "Tanh": _lib.UN_TANH, "Erf": _lib.UN_ERF, "Sin": _lib.UN_SIN, "Cos": _lib.UN_COS, "Powf": _lib.UN_POWF,
-          "AddScalar": _lib.UN_ADD_SCALAR, "MulScalar": _lib.UN_MUL_SCALAR}
-_BINARY = {"Add": _lib.BIN_ADD, "Sub": _lib.BIN_SUB, "Mul": _lib.BIN_MUL, "Div": _lib.BIN_DIV, "Maximum": _lib.BIN_MAXIMUM}
+          "AddScalar": _lib.UN_ADD_SCALAR, "MulScalar": _lib.UN_MUL_SCALAR, "Log": _lib.UN_LOG, "Abs": _lib.UN_ABS,
+          "Sign": _lib.UN_SIGN, "Log2": _lib.UN_LOG2, "Log10": _lib.UN_LOG10}
+_BINARY = {"Add": _lib.BIN_ADD, "Sub": _lib.BIN_SUB, "Mul": _lib.BIN_MUL, "Div": _lib.BIN_DIV, "Maximum": _lib.BIN_MAXIMUM,
+           "Minimum": _lib.BIN_MINIMUM}
+_COMPARE = {"Equal": _lib.CMP_EQ, "NotEqual": _lib.CMP_NE, "Greater": _lib.CMP_GT, "GreaterEqual": _lib.CMP_GE,
+            "Less": _lib.CMP_LT, "LessEqual": _lib.CMP_LE}
 
 
 def _unary_rule(code):
@@ -367,7 +432,21 @@ def _softmax(x: Tensor, dim: int) -> Tensor:
 
 
 def _reduce_rule(code):
-    def rule(x: Tensor, dim: int, keep_dim: bool) -> Tensor:
+    def rule(x: Tensor, dim, keep_dim: bool) -> Tensor:
+        if not isinstance(dim, int):
+            # ReduceSum{dims, keep_dim} over any set of dims (ops/reduce_sum.rs:63-76): the reduced dims are moved to
+            # the end and flattened into one, then it is a row reduction
+            r = len(x.shape)
+            dims = sorted({_resolve_dim(d, r) for d in dim})
+            kept = [i for i in range(r) if i not in dims]
+            order = kept + dims
+            moved_x = x._view([x.shape[i] for i in order], [x.strides[i] for i in order], x.offset).contiguous()
+            cols = int(np.prod([x.shape[i] for i in dims])) if dims else 1
+            flat = moved_x.reshape([x.shape[i] for i in kept] + [cols])
+            out = rule(flat, -1, False)
+            if keep_dim:
+                out = out.reshape([1 if i in dims else x.shape[i] for i in range(r)])
+            return out
         xs, moved, d = _rows_last(x, dim)
         cols = xs.shape[-1]
         out = Tensor._alloc(xs.shape[:-1], xs.dtype, xs.device)
@@ -387,8 +466,10 @@ def _index_select(x: Tensor, dim: int, index: Tensor) -> Tensor:
 
 
 def _gather(x: Tensor, dim: int, index: Tensor) -> Tensor:
-    if _resolve_dim(dim, len(x.shape)) != len(x.shape) - 1:
-        raise _lib.RaiB200Error(-7, "gather along a dim other than the last")
+    d = _resolve_dim(dim, len(x.shape))
+    if d != len(x.shape) - 1:   # move the gathered dim last on both operands, gather, move it back
+        last = len(x.shape) - 1
+        return _gather(x.transpose(d, last), -1, index.transpose(d, last)).transpose(d, last)
     xd, idx = x.contiguous(), index.contiguous()
     out = Tensor._alloc(idx.shape, xd.dtype, xd.device)
     _lib.call("rb_gather_last", xd.device.ctx, xd.ptr(), xd.numel() // xd.shape[-1], xd.shape[-1], idx.ptr(), idx.shape[-1],
@@ -444,6 +525,98 @@ def _arange(device: Cuda, start: float, stop: float, step: float, dtype: int) ->
     return out
 
 
+def _compare_rule(code):
+    def rule(a: Tensor, b) -> Tensor:
+        if not isinstance(b, Tensor):
+            b = Tensor.full(float(b), [], a.dtype, a.device)
+        shape = list(np.broadcast_shapes(tuple(a.shape), tuple(b.shape)))
+        a, b = a.broadcast_to(shape), b.broadcast_to(shape)
+        if len(shape) > 4:
+            a, b = a.contiguous().reshape([-1]), b.contiguous().reshape([-1])
+        out = Tensor._alloc(shape, _lib.U8, a.device)
+        _lib.call("rb_compare", a.device.ctx, code, a.ptr(), _i64(a.strides), b.ptr(), _i64(b.strides), out.ptr(), len(a.shape),
+                  _i64(a.shape), a.dtype)
+        return out
+    return rule
+
+
+def _log_softmax(x: Tensor, dim: int) -> Tensor:
+    xs, moved, d = _rows_last(x, dim)
+    out = Tensor._alloc(xs.shape, xs.dtype, xs.device)
+    cols = xs.shape[-1]
+    _lib.call("rb_log_softmax_rows", xs.device.ctx, xs.ptr(), out.ptr(), xs.numel() // cols, cols, xs.dtype)
+    if moved:
+        r = len(out.shape)
+        order = list(range(d)) + [r - 1] + list(range(d, r - 1))
+        out = out._view([out.shape[i] for i in order], [out.strides[i] for i in order], out.offset)
+    return out
+
+
+def _argmin(x: Tensor, dim: int) -> Tensor:
+    xs, _, _ = _rows_last(x, dim)
+    out = Tensor._alloc(xs.shape[:-1], _lib.U32, xs.device)
+    _lib.call("rb_argmin_rows", xs.device.ctx, xs.ptr(), xs.dtype, xs.numel() // xs.shape[-1], xs.shape[-1], out.ptr())
+    return out
+
+
+def _scatter_rule(index_is_1d: bool):
+    def rule(x: Tensor, source: Tensor, index: Tensor, dim: int) -> Tensor:
+        """Inputs in the reference's order: x, source/updates, index (candle.rs:853-855, 993-995)."""
+        d = _resolve_dim(dim, len(x.shape))
+        xd, sd, idx = x.contiguous(), source.contiguous(), index.contiguous()
+        outer = int(np.prod(xd.shape[:d])) if d else 1
+        inner = int(np.prod(xd.shape[d + 1:])) if d + 1 < len(xd.shape) else 1
+        out = Tensor._alloc(xd.shape, xd.dtype, xd.device)
+        _lib.call("rb_scatter_add", xd.device.ctx, xd.ptr(), sd.ptr(), idx.ptr(), out.ptr(), outer, xd.shape[d], sd.shape[d],
+                  inner, int(index_is_1d), xd.dtype)
+        return out
+    return rule
+
+
+def _i32(xs: Sequence[int]):
+    return (ctypes.c_int32 * max(1, len(xs)))(*[int(v) for v in xs])
+
+
+def _conv2d(x: Tensor, w: Tensor, padding, stride, dilation) -> Tensor:
+    xd, wd = x.contiguous(), w.contiguous()
+    shape = (ctypes.c_int32 * 4)()
+    args = (xd.device.ctx, xd.ptr(), _i32(xd.shape), wd.ptr(), _i32(wd.shape), _i32(padding), _i32(stride), _i32(dilation))
+    _lib.call("rb_conv2d", *args, None, shape, xd.dtype)            # shape query
+    out = Tensor._alloc(list(shape), xd.dtype, xd.device)
+    _lib.call("rb_conv2d", *args, out.ptr(), shape, xd.dtype)
+    return out
+
+
+def _conv_transpose2d(x: Tensor, w: Tensor, padding, out_padding, stride, dilation) -> Tensor:
+    xd, wd = x.contiguous(), w.contiguous()
+    shape = (ctypes.c_int32 * 4)()
+    args = (xd.device.ctx, xd.ptr(), _i32(xd.shape), wd.ptr(), _i32(wd.shape), _i32(padding), _i32(out_padding), _i32(stride),
+            _i32(dilation))
+    _lib.call("rb_conv_transpose2d", *args, None, shape, xd.dtype)
+    out = Tensor._alloc(list(shape), xd.dtype, xd.device)
+    _lib.call("rb_conv_transpose2d", *args, out.ptr(), shape, xd.dtype)
+    return out
+
+
+def _pool_rule(is_max: bool):
+    def rule(x: Tensor, kernel, stride, padding, dilation=(1, 1)) -> Tensor:
+        xd = x.contiguous()
+        shape = (ctypes.c_int32 * 4)()
+        args = (xd.device.ctx, int(is_max), xd.ptr(), _i32(xd.shape), _i32(kernel), _i32(stride), _i32(padding), _i32(dilation))
+        _lib.call("rb_pool2d", *args, None, shape, xd.dtype)
+        out = Tensor._alloc(list(shape), xd.dtype, xd.device)
+        _lib.call("rb_pool2d", *args, out.ptr(), shape, xd.dtype)
+        return out
+    return rule
+
+
+def _upsample_nearest2d(x: Tensor, size) -> Tensor:
+    xd = x.contiguous()
+    out = Tensor._alloc(xd.shape[:2] + [int(size[0]), int(size[1])], xd.dtype, xd.device)
+    _lib.call("rb_upsample_nearest2d", xd.device.ctx, xd.ptr(), _i32(xd.shape), int(size[0]), int(size[1]), out.ptr(), xd.dtype)
+    return out
+
+
 def register_all() -> None:
     """The `register_backend!` list (rai-core/src/dispatch.rs:41-157) for the ops the decoders reach."""
     for name, code in _UNARY.items():
@@ -464,6 +637,17 @@ def register_all() -> None:
     register(Cuda, "ToDType", _to_dtype)
     register(Cuda, "Full", _full)
     register(Cuda, "Arange", _arange)
+    for name, code in _COMPARE.items():
+        register(Cuda, name, _compare_rule(code))
+    register(Cuda, "LogSoftmax", _log_softmax)
+    register(Cuda, "ArgMin", _argmin)
+    register(Cuda, "ScatterAdd", _scatter_rule(False))
+    register(Cuda, "IndexAdd", _scatter_rule(True))
+    register(Cuda, "Conv2d", _conv2d)
+    register(Cuda, "ConvTranspose2d", _conv_transpose2d)
+    register(Cuda, "MaxPool2d", _pool_rule(True))
+    register(Cuda, "AvgPool2d", _pool_rule(False))
+    register(Cuda, "UpsampleNearest2d", _upsample_nearest2d)
 
 
 register_all()

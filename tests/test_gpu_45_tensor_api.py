@@ -117,7 +117,7 @@ def test_scalar_ops_activations_where_gather(cuda):
 
 def test_dispatch_registry_reports_missing_rules_and_can_be_overridden(cuda):
     with pytest.raises(_lib.RaiB200Error) as e:
-        eval_rule(cuda, "Conv2d")          # Error::Unimplemented{op, device} (eval.rs:40-43)
+        eval_rule(cuda, "Random")          # Error::Unimplemented{op, device} (eval.rs:40-43)
     assert e.value.code == -7
     calls = []
     old = eval_rule(cuda, "Negative")
