@@ -197,11 +197,11 @@ int32_t rb_attention(rb_ctx* ctx, const void* q_dev, rb_kv_cache* cache, int32_t
  * bf16 only, for callers that must not trigger a device allocation: rb_attention grows its split-KV
  * scratch with cudaMalloc when a larger shape arrives, which is off limits to a host runtime that owns
  * all device memory through its own pool, and unwelcome in a serving loop because an allocation can
- * synchronise the whole device.  This variant keeps that scratch in a 4 MiB array built into the
+ * synchronise the whole device.  This variant keeps that scratch in a 2 MiB array built into the
  * library (held by every GPU that loads it, until exit) and calls neither cudaMalloc nor cudaFree nor any
  * allocating library routine.  (The CUDA runtime itself may still load a kernel's code the first time that
  * kernel is launched: make the first call per head size before the host's pool takes the remaining memory.)
- *   - limit: batch * q_heads * splits * (head_dim + 2) floats must fit in 1 Mi floats; larger shapes are
+ *   - limit: batch * q_heads * splits * (head_dim + 2) floats must fit in 512 Ki floats; larger shapes are
  *     rejected with RB_ERR_INVALID and a message naming the sizes (use rb_attention for those);
  *   - the first call on a device looks up the array's device address (one cudaGetSymbolAddress, the
  *     context's device must be current; the look-up is guarded by a lock, so first calls from several threads are

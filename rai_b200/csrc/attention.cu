@@ -537,18 +537,43 @@ attention_kernel(const AParams p, const __grid_constant__ CUtensorMap tm_k, cons
   }
   __syncthreads();
   if (!is_last) return;
+  // The per-split maxima and sums of this block's rows first (a few hundred floats, one round trip to L2), turned
+  // into one weight per (row, split) in shared memory; then every output element sums its splits with all loads in
+  // flight at once.  Same sums, in the same split order, as attention_merge_kernel.
+  float* w_s = reinterpret_cast<float*>(smem);          // [16 rows][32 splits] weights exp2(M_split - M) / L
+  const int ns = p.n_splits;                             // <= 32
+  for (int i = threadIdx.x; i < p.group * ns; i += blockDim.x) {
+    const int row = i / ns, sp = i % ns;
+    const size_t bh = (size_t)b * p.q_heads + head + row;
+    w_s[row * 32 + sp] = __ldcg(p.part_ml + (bh * ns + sp) * 2);            // max, for now
+    w_s[512 + row * 32 + sp] = __ldcg(p.part_ml + (bh * ns + sp) * 2 + 1);  // sum
+  }
+  __syncthreads();
+  if (threadIdx.x < p.group) {
+    const int row = threadIdx.x;
+    float M = -INFINITY;
+    for (int sp = 0; sp < ns; ++sp) M = fmaxf(M, w_s[row * 32 + sp]);
+    const float Mu = (M == -INFINITY) ? 0.f : M;
+    float L = 0.f;
+    for (int sp = 0; sp < ns; ++sp) L += w_s[512 + row * 32 + sp] * exp2f(w_s[row * 32 + sp] - Mu);
+    for (int sp = 0; sp < ns; ++sp) w_s[row * 32 + sp] = exp2f(w_s[row * 32 + sp] - Mu);
+    w_s[1024 + row] = L;
+  }
+  __syncthreads();
   for (int idx = threadIdx.x; idx < p.group * D; idx += blockDim.x) {
     const int row = idx / D, dd = idx % D;
     const size_t bh = (size_t)b * p.q_heads + head + row;
-    const float* ml_p = p.part_ml + bh * p.n_splits * 2;
-    const float* o_p = p.part_o + bh * p.n_splits * D;
-    float M = -INFINITY;
-    for (int sp = 0; sp < p.n_splits; ++sp) M = fmaxf(M, __ldcg(ml_p + sp * 2));
-    const float Mu = (M == -INFINITY) ? 0.f : M;
-    float L = 0.f, O = 0.f;
-    for (int sp = 0; sp < p.n_splits; ++sp) L += __ldcg(ml_p + sp * 2 + 1) * exp2f(__ldcg(ml_p + sp * 2) - Mu);
-    for (int sp = 0; sp < p.n_splits; ++sp) O += __ldcg(o_p + (size_t)sp * D + dd) * exp2f(__ldcg(ml_p + sp * 2) - Mu);
-    p.out[bh * D + dd] = __float2bfloat16_rn(O / L);
+    const float* o_p = p.part_o + bh * ns * D + dd;
+    float O = 0.f;
+    for (int s0 = 0; s0 < ns; s0 += 8) {
+      float t[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) t[k] = (s0 + k < ns) ? __ldcg(o_p + (size_t)(s0 + k) * D) : 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (s0 + k < ns) O += t[k] * w_s[row * 32 + s0 + k];
+    }
+    p.out[bh * D + dd] = __float2bfloat16_rn(O / w_s[1024 + row]);
   }
 }
 
@@ -629,11 +654,11 @@ int launch_attention(rb_ctx* ctx, rb_kv_cache* c, AParams& p, int batch, int max
 // a host runtime that hands all device memory to its own pool and treats a foreign cudaMalloc as
 // an error, or a serving loop that cannot afford the device-wide synchronisation an allocation may
 // imply.  For them the same kernels run here with the partials in a fixed array that is part of
-// the library image: every GPU that loads the library holds these 4 MiB until the process exits.
+// the library image: every GPU that loads the library holds these 2 MiB until the process exits.
 // (What the entry point cannot rule out is the CUDA runtime loading a kernel's code on its first
 // launch; a caller whose pool takes all remaining memory makes one call per head size first.)
 // ------------------------------------------------------------------------------------------
-constexpr size_t kStaticScratchFloats = 1u << 20;  // 4 MiB
+constexpr size_t kStaticScratchFloats = 1u << 19;  // 2 MiB
 static __device__ __align__(256) float g_static_attn_scratch[kStaticScratchFloats];
 // In host code the array's name is only a handle for the runtime, not a device address: the address
 // the kernels need is asked for once per device (with that device current) and kept here.

@@ -62,19 +62,24 @@ struct rb_kv_cache {
   size_t layer_stride_elems() const { return (size_t)num_pages * kv_heads * 64 * head_dim; }
 };
 
-// Peer-memory exchange of a tensor-parallel group for decode-sized allreduces: every rank pushes its
-// partial [rows, hidden] into its own place in EVERY rank's exchange buffer (posted stores over NVLink,
-// no round trip) and then raises a flag in every peer's flag array; the consumer waits (bounded) for
-// all flags and sums the copies in its own memory in rank order, the same on every rank.  Two slots,
-// chosen by the parity of a device-side sequence number, so replayed CUDA graphs need no new arguments.
+// Peer-memory exchange of a tensor-parallel group for decode-sized allreduces: every rank pushes its partial
+// [rows, hidden] into its own place in EVERY rank's exchange buffer (posted stores over NVLink, no round trip); the
+// block that pushed row r then raises, after one system-scope fence, the flag of (source rank, row r) in every peer's
+// flag array, waits (bounded) for that row's flag from every rank - it does not wait for the other rows - and sums
+// the copies in its own memory in rank order, the same on every rank.  Two slots, chosen by the parity of an exchange
+// number kept on the device, so replayed CUDA graphs need no new arguments: launches alternate between two local
+// counters (a launch reads one and sets the other for its successor), so no kernel changes a word its own blocks are
+// still reading.  Slot n & 1 is free again when exchange n + 2 starts: a rank gets there only after every rank has
+// raised its flags of exchange n + 1, which a rank does only after its own exchange n has completed.
 constexpr int kGemmMaxReduceTiles = 256;
+
 constexpr int kTpMaxRanks = 8;
 constexpr int kTpMaxRows = 256;
+constexpr size_t kTpFlagBytes = (size_t)2 * kTpMaxRanks * kTpMaxRows * sizeof(uint32_t);  // [2 slots][source rank][row]
 struct TpPeers {
   const void* xbuf[kTpMaxRanks];   // every rank's exchange buffer (own included), [2 slots][size sources][kTpMaxRows][hidden]
-  uint32_t* flags[kTpMaxRanks];    // every rank's flag array, [2][kTpMaxRanks]
-  uint32_t* seq;                   // local: number of exchanges published so far
-  uint32_t* block_count;           // local: arrival counter of the publishing kernel
+  uint32_t* flags[kTpMaxRanks];    // every rank's flag array, [2][kTpMaxRanks][kTpMaxRows]
+  uint32_t* seq;                   // local: two exchange counters 128 bytes apart, seq[0] for even launches, seq[32] for odd
   int rank, size;
   int64_t slot_elems;              // kTpMaxRows * hidden
 };
@@ -116,7 +121,6 @@ struct GemmArgs {
   int act = RB_ACT_NONE;
   int n_split = 1;              // > 1: write float partials, no epilogue
   bool partials = false;
-  const TpPeers* push = nullptr;  // M <= 64: the result goes into this rank's place in every peer's exchange buffer
   bool reduce = false;            // M <= 64: if K is split, sum the splits inside the kernel and apply the epilogue
 };
 int gemm_tc_bf16(rb_ctx* ctx, const GemmArgs& a);
@@ -126,11 +130,12 @@ int gemm_simple(rb_ctx* ctx, const GemmArgs& a, int dtype);
 
 int attention_mma_bf16(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, int batch, int s_new, int q_heads,
                        float scale, void* out);
-// decoder_kernels.cu: publish this rank's partial sum / norm with the peers' partials folded in.
-int tp_publish(rb_ctx* ctx, const TpPeers& tp, const float* acc, int n_acc, const void* bias, const void* x, int64_t rows,
-               int64_t hidden);
-int norm_tp(rb_ctx* ctx, const TpPeers& tp, int kind, const void* x, const void* w, const void* b, float eps, int64_t rows,
-            int64_t hidden, void* out, void* sum_out);
+// decoder_kernels.cu: the tensor-parallel sum of a row-parallel product (split-K slabs + bias, or a finished bf16
+// tensor `part`) over the exchange buffers, the residual add and the following norm, in one kernel.
+// sum_out = h + sum over ranks; out = norm(sum_out) (out may be NULL).  `parity` alternates 0,1,0,1.. launch by launch.
+int exchange_norm(rb_ctx* ctx, const TpPeers& tp, int parity, int kind, const void* h, const float* acc, int n_acc,
+                  const void* acc_bias, const void* part, const void* w, const void* b, float eps, int64_t rows,
+                  int64_t hidden, void* out, void* sum_out);
 // decoder_kernels.cu: out[r, j] = act(sum_s part[s][r][j] + bias[j]) (* sum_s part[s][r][j + n_out] when gated)
 int act_from_partials(rb_ctx* ctx, const float* part, int n_split, int64_t rows, int64_t n_all, int64_t n_out, bool gated,
                       const void* bias, int act, void* out);

@@ -118,23 +118,23 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
 
 // 16 bytes of this rank's exchange buffer, which its peers write over NVLink: read at system scope so that no
 // stale L1 line can serve it
-__device__ __forceinline__ void load8_sys(const __nv_bfloat16* p, float* v) {
+__device__ __forceinline__ uint4 load16_sys(const void* p) {
   uint4 u;
   asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "l"(p) : "memory");
+  return u;
+}
+__device__ __forceinline__ void add8_bf16(const uint4& u, float* v) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] += f.x; v[2 * i + 1] += f.y; }
 }
-__device__ __forceinline__ void load8_sys(const float* p, float* v) { load8(p, v); }  // exchange buffers are bf16 only
 
-template <typename T, int kChunks, bool TP>
+template <typename T, int kChunks>
 __global__ void __launch_bounds__(512) norm_vec_kernel(int kind, const T* __restrict__ x, const T* __restrict__ add,
                                 const float* __restrict__ acc, int n_acc, size_t acc_stride,
                                 const T* __restrict__ acc_bias, const T* __restrict__ w, const T* __restrict__ b,
-                                float eps, int hidden, T* __restrict__ out, T* __restrict__ sum_out, const TpPeers tp,
-                                uint32_t* status, long long wait_cycles) {
+                                float eps, int hidden, T* __restrict__ out, T* __restrict__ sum_out, int64_t n_rows) {
   __shared__ float red[32];
-  __shared__ uint32_t tp_seq_s;
   pdl_launch_dependents();
   float wv[kChunks][8], bv[kChunks][8];
   const int nchunk = hidden >> 3;
@@ -150,28 +150,10 @@ __global__ void __launch_bounds__(512) norm_vec_kernel(int kind, const T* __rest
     }
   }
   pdl_wait();
-  const size_t base = (size_t)blockIdx.x * hidden;
-  size_t tp_off = 0;
-  if (TP) {
-    // every rank has published exchange number `seq` when its flag in MY array says so; bounded wait
-    if (threadIdx.x == 0) {
-      const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(tp.seq);
-      const uint32_t* mine = tp.flags[tp.rank] + (seq & 1u) * kTpMaxRanks;
-      const long long t0 = clock64();
-      bool ok = true;
-      for (int r = 0; r < tp.size && ok; ++r) {
-        while (ld_acquire_sys(mine + r) < seq) {
-          if (clock64() - t0 > wait_cycles) { ok = false; break; }
-        }
-      }
-      if (!ok) { status[0] = (uint32_t)(-RB_ERR_TIMEOUT); status[1] = 0x7A11u; status[2] = (uint32_t)tp.rank; status[3] = seq; }
-      tp_seq_s = ok ? seq : 0xffffffffu;
-    }
-    __syncthreads();
-    if (tp_seq_s == 0xffffffffu) return;  // a peer never arrived: leave the outputs alone, the host sees the status
-    // thread 0's acquire loads plus the barrier order every thread's (system-scope) reads below behind the flags
-    tp_off = (size_t)(tp_seq_s & 1u) * tp.size * tp.slot_elems;
-  }
+  // One block may take several rows (prefill launches fewer blocks than rows: the weights stay in registers and the
+  // block's start-up is paid once).
+  auto do_row = [&](int64_t row) {
+  const size_t base = (size_t)row * hidden;
   float v[kChunks][8];
   float s = 0.f;
   const float inv_sqrt_h = 1.0f / sqrtf((float)hidden);
@@ -192,23 +174,6 @@ __global__ void __launch_bounds__(512) norm_vec_kernel(int kind, const T* __rest
     if (acc_bias) { load8(acc_bias + ch * 8, t);
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[c][i] += t[i]; }
-    if (TP) {  // every rank's partial sum, pushed into THIS rank's buffer by its owner, added in rank order on every rank alike
-      float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      const T* mine = reinterpret_cast<const T*>(tp.xbuf[tp.rank]) + tp_off + base + ch * 8;
-      float pr[kTpMaxRanks][8];
-#pragma unroll
-      for (int r = 0; r < kTpMaxRanks; ++r)
-        if (r < tp.size) load8_sys(mine + (size_t)r * tp.slot_elems, pr[r]);
-#pragma unroll
-      for (int r = 0; r < kTpMaxRanks; ++r)
-        if (r < tp.size) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) sum[i] += pr[r][i];
-        }
-      round_to<T>(sum);  // what an allreduce in the model dtype would have delivered
-#pragma unroll
-      for (int i = 0; i < 8; ++i) v[c][i] += sum[i];
-    }
     round_to<T>(v[c]);  // the residual stream is stored in the model dtype
     if (sum_out) store8(sum_out + base + ch * 8, v[c]);
 #pragma unroll
@@ -250,52 +215,152 @@ __global__ void __launch_bounds__(512) norm_vec_kernel(int kind, const T* __rest
     }
     store8(out + base + ch * 8, y);
   }
+  };
+  for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) do_row(row);
 }
 
 
-// Tensor-parallel publish: this rank's partial product (split-K slabs + bias, or a finished tensor x)
-// is pushed into this rank's place of the next slot in EVERY rank's exchange buffer; the last block to
-// finish bumps the sequence number and raises this rank's flag in every peer's flag array.
-template <typename T>
-__global__ void __launch_bounds__(512) tp_publish_kernel(const float* __restrict__ acc, int n_acc, size_t acc_stride, const T* __restrict__ bias,
-                                  const T* __restrict__ x, int hidden, const TpPeers tp) {
-  __shared__ uint32_t last_block;
+// Tensor-parallel allreduce of a row-parallel product, fused with the residual add and the norm that follow it.  One
+// block per row: it finishes this rank's partial row (split-K slabs + bias, or a bf16 tensor), pushes it into this
+// rank's place of the next slot in EVERY rank's exchange buffer (posted stores over NVLink, nobody waits for a reply),
+// raises that row's flag on every peer, then waits (bounded) for the same row from every rank, sums the copies that
+// now sit in its OWN memory in rank order - the same on every rank - adds the residual stream and normalises.  A row
+// waits only for that row: no block waits for another block of its own kernel.
+//
+// Exchange numbers live on the device so that a captured graph replays unchanged: a launch with parity q reads
+// counter[q] (exchange number = counter[q] + 1) and, when done, sets counter[q ^ 1] to that number for the next
+// launch, whose parity is the opposite one; no launch writes the counter its own blocks read.
+template <typename T, int kChunks>
+__global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* __restrict__ h, const float* __restrict__ acc, int n_acc,
+                                     size_t acc_stride, const T* __restrict__ acc_bias, const T* __restrict__ part,
+                                     const T* __restrict__ w, const T* __restrict__ b, float eps, int hidden,
+                                     T* __restrict__ out, T* __restrict__ sum_out, const TpPeers tp, int parity,
+                                     uint32_t* status, long long wait_cycles) {
+  __shared__ float red[32];
+  __shared__ uint32_t give_up;
   pdl_launch_dependents();
+  float wv[kChunks][8], bv[kChunks][8];
+  const int nchunk = hidden >> 3;
+  // weights do not depend on the previous kernel: fetch them before waiting for it
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { wv[c][i] = 1.f; bv[c][i] = 0.f; }
+    if (ch < nchunk && out) {
+      if (w) load8(w + ch * 8, wv[c]);
+      if (b) load8(b + ch * 8, bv[c]);
+    }
+  }
+  if (threadIdx.x == 0) give_up = 0u;
   pdl_wait();
-  const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(tp.seq) + 1u;
-  // slot (seq & 1), source `rank`, inside every rank's buffer: [2 slots][size sources][rows x hidden]
-  const size_t dst_off = ((size_t)(seq & 1u) * tp.size + tp.rank) * tp.slot_elems;
-  const size_t base = (size_t)blockIdx.x * hidden;
-  for (int ch = threadIdx.x; ch < (hidden >> 3); ch += blockDim.x) {
+  const int row = blockIdx.x;
+  const size_t base = (size_t)row * hidden;
+  const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(tp.seq + parity * 32) + 1u;
+  const size_t slot_off = (size_t)(seq & 1u) * tp.size * tp.slot_elems;   // [2 slots][size sources][rows x hidden]
+  // ---- this rank's partial row, rounded to the model dtype, into every rank's buffer
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch >= nchunk) continue;
     float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, t[8];
-    if (x) { load8(x + base + ch * 8, t);
+    if (part) { load8(part + base + ch * 8, t);
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[i] += t[i]; }
     add_slabs(acc, n_acc, acc_stride, base + ch * 8, v);
-    if (bias) { load8(bias + ch * 8, t);
+    if (acc_bias) { load8(acc_bias + ch * 8, t);
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[i] += t[i]; }
-    // the same 16 bytes into every rank's copy: posted stores over NVLink, nobody waits for a reply
     const uint4 packed = pack8_bf16(v);
 #pragma unroll
     for (int r = 0; r < kTpMaxRanks; ++r)
       if (r < tp.size)
-        *reinterpret_cast<uint4*>(reinterpret_cast<T*>(const_cast<void*>(tp.xbuf[r])) + dst_off + base + ch * 8) = packed;
+        *reinterpret_cast<uint4*>(reinterpret_cast<T*>(const_cast<void*>(tp.xbuf[r])) + slot_off + (size_t)tp.rank * tp.slot_elems +
+                                  base + ch * 8) = packed;
   }
-  __syncthreads();  // the block's stores are ordered before thread 0's fence (cumulativity through the barrier)
-  if (threadIdx.x == 0) {
-    __threadfence_system();  // this block's stores to the peers are performed before it is counted
-    const unsigned int arrived = atomicAdd(tp.block_count, 1u);
-    last_block = (arrived == gridDim.x - 1) ? 1u : 0u;
-    if (last_block) {
-      *tp.block_count = 0u;
-      *reinterpret_cast<volatile uint32_t*>(tp.seq) = seq;
-      __threadfence_system();  // one system-scope fence, then plain flag stores to all peers in parallel
+  __syncthreads();  // the block's stores are ordered before the fences below (cumulativity through the barrier)
+  if ((int)threadIdx.x < tp.size) {
+    __threadfence_system();  // this row is performed at every peer before its flag can be seen there
+    st_release_sys(tp.flags[threadIdx.x] + ((size_t)(seq & 1u) * kTpMaxRanks + tp.rank) * kTpMaxRows + row, seq);
+    // ---- and the same row from every rank: thread t waits for rank t
+    const uint32_t* flag = tp.flags[tp.rank] + ((size_t)(seq & 1u) * kTpMaxRanks + threadIdx.x) * kTpMaxRows + row;
+    const long long t0 = clock64();
+    while ((int32_t)(ld_acquire_sys(flag) - seq) < 0) {
+      if (clock64() - t0 > wait_cycles) {
+        status[0] = (uint32_t)(-RB_ERR_TIMEOUT); status[1] = 0x7A11u; status[2] = (uint32_t)tp.rank; status[3] = seq;
+        give_up = 1u;
+        break;
+      }
     }
   }
   __syncthreads();
-  if (last_block && threadIdx.x < tp.size)
-    *reinterpret_cast<volatile uint32_t*>(tp.flags[threadIdx.x] + (seq & 1u) * kTpMaxRanks + tp.rank) = seq;
+  // the exchange number moves on whether or not a peer arrived: the next launch must not reuse this one's slot
+  if (row == 0 && threadIdx.x == 0) *reinterpret_cast<volatile uint32_t*>(tp.seq + (parity ^ 1) * 32) = seq;
+  if (give_up) return;  // a peer never arrived: leave the outputs alone, the host sees the status
+  // the pollers' acquire loads plus the barrier order every thread's (system-scope) reads below behind the flags
+  float v[kChunks][8];
+  float s = 0.f;
+  const float inv_sqrt_h = 1.0f / sqrtf((float)hidden);
+  const T* mine = reinterpret_cast<const T*>(tp.xbuf[tp.rank]) + slot_off + base;
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[c][i] = 0.f;
+    if (ch >= nchunk) continue;
+    uint4 pr[kTpMaxRanks];  // all copies in flight at once, still packed
+    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < kTpMaxRanks; ++r)
+      if (r < tp.size) pr[r] = load16_sys(mine + (size_t)r * tp.slot_elems + ch * 8);
+    if (h) load8(h + base + ch * 8, v[c]);
+#pragma unroll
+    for (int r = 0; r < kTpMaxRanks; ++r)   // rank order, on every rank alike
+      if (r < tp.size) add8_bf16(pr[r], sum);
+    round_to<T>(sum);  // what an allreduce in the model dtype would have delivered
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[c][i] += sum[i];
+    round_to<T>(v[c]);  // the residual stream is stored in the model dtype
+    if (sum_out) store8(sum_out + base + ch * 8, v[c]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (kind == RB_NORM_LAYER) s += v[c][i];
+      else if (kind == RB_NORM_RMS) { const float t2 = v[c][i] * inv_sqrt_h; s += t2 * t2; }
+      else s += v[c][i] * v[c][i];
+    }
+  }
+  if (!out) return;
+  s = block_sum(s, red);
+  float mean = 0.f, r;
+  if (kind == RB_NORM_LAYER) {
+    mean = s / (float)hidden;
+    float q = 0.f;
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c)
+      if (threadIdx.x + c * blockDim.x < nchunk) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { const float d = v[c][i] - mean; q += d * d; }
+      }
+    q = block_sum(q, red);
+    r = 1.0f / sqrtf(q / (float)hidden + eps);
+  } else if (kind == RB_NORM_RMS) {
+    r = 1.0f / sqrtf(s + eps);
+  } else {
+    r = 1.0f / sqrtf(s / (float)hidden + eps);
+  }
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch >= nchunk) continue;
+    float y[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (kind == RB_NORM_LAYER) { y[i] = (v[c][i] - mean) * r; if (w) y[i] = wv[c][i] * y[i] + bv[c][i]; }
+      else if (kind == RB_NORM_RMS) y[i] = wv[c][i] * v[c][i] * r;
+      else y[i] = v[c][i] * r * (wv[c][i] + 1.0f);
+    }
+    store8(out + base + ch * 8, y);
+  }
 }
 
 
@@ -629,7 +694,7 @@ extern "C" int32_t rb_embed_gather(rb_ctx* ctx, const void* table, int32_t dtype
 template <typename T>
 static int norm_launch(rb_ctx* ctx, int kind, const void* x, const void* add, const float* acc, int n_acc,
                        const void* acc_bias, const void* w, const void* b, float eps, int64_t rows, int64_t hidden,
-                       void* out, void* sum_out, const TpPeers* tp = nullptr) {
+                       void* out, void* sum_out) {
   const size_t acc_stride = (size_t)rows * hidden;
   const bool vec_ok = (hidden % 8) == 0 && hidden <= 16384 && aligned16(x) && aligned16(add) && aligned16(acc) &&
                       aligned16(acc_bias) && aligned16(w) && aligned16(b) && aligned16(out) && aligned16(sum_out) &&
@@ -638,23 +703,18 @@ static int norm_launch(rb_ctx* ctx, int kind, const void* x, const void* add, co
     const int nchunk = (int)(hidden / 8);
     int threads = std::min(512, (nchunk + 31) / 32 * 32);
     const int chunks = (nchunk + threads - 1) / threads;
+    // decode-sized calls get a block per row (pure latency); prefill-sized ones a few blocks per SM that walk the rows
+    const int64_t blocks = std::min<int64_t>(rows, (int64_t)ctx->sm_count * 4);
     auto go = [&](auto kern) {
-      return launch_kernel(kern, dim3((unsigned)rows), dim3(threads), 0, ctx->stream, ctx->pdl, kind, (const T*)x,
+      return launch_kernel(kern, dim3((unsigned)blocks), dim3(threads), 0, ctx->stream, ctx->pdl, kind, (const T*)x,
                            (const T*)add, acc, n_acc, acc_stride, (const T*)acc_bias, (const T*)w, (const T*)b, eps,
-                           (int)hidden, (T*)out, (T*)sum_out, tp ? *tp : TpPeers{}, ctx->status_dev, ctx->wait_budget_cycles);
+                           (int)hidden, (T*)out, (T*)sum_out, (int64_t)rows);
     };
-    if (tp) {
-      if (chunks == 1) RB_CUDA(go(norm_vec_kernel<T, 1, true>));
-      else if (chunks == 2) RB_CUDA(go(norm_vec_kernel<T, 2, true>));
-      else RB_CUDA(go(norm_vec_kernel<T, 4, true>));
-    } else {
-      if (chunks == 1) RB_CUDA(go(norm_vec_kernel<T, 1, false>));
-      else if (chunks == 2) RB_CUDA(go(norm_vec_kernel<T, 2, false>));
-      else RB_CUDA(go(norm_vec_kernel<T, 4, false>));
-    }
+    if (chunks == 1) RB_CUDA(go(norm_vec_kernel<T, 1>));
+    else if (chunks == 2) RB_CUDA(go(norm_vec_kernel<T, 2>));
+    else RB_CUDA(go(norm_vec_kernel<T, 4>));
     return RB_OK;
   }
-  if (tp) return fail(RB_ERR_INVALID, "tensor-parallel norm needs hidden %% 8 == 0 and 16-byte aligned operands");
   const size_t smem = (size_t)hidden * sizeof(float);
   const int threads = hidden >= 2048 ? 512 : 256;
   auto kern = norm_kernel<T>;
@@ -692,11 +752,30 @@ extern "C" int32_t rb_norm(rb_ctx* ctx, int32_t kind, const void* x, const void*
 
 namespace rb {
 
-int norm_tp(rb_ctx* ctx, const TpPeers& tp, int kind, const void* x, const void* w, const void* b, float eps, int64_t rows,
-            int64_t hidden, void* out, void* sum_out) {
-  RB_REQUIRE(rows > 0 && rows <= kTpMaxRows, "norm_tp: %lld rows exceed the exchange buffer", (long long)rows);
-  ProfScope prof(ctx, RB_PROF_NORM, (double)rows * hidden * 2.0 * (3 + tp.size), 0.0);
-  RB_TRY(norm_launch<__nv_bfloat16>(ctx, kind, x, nullptr, nullptr, 0, nullptr, w, b, eps, rows, hidden, out, sum_out, &tp));
+int exchange_norm(rb_ctx* ctx, const TpPeers& tp, int parity, int kind, const void* h, const float* acc, int n_acc,
+                  const void* acc_bias, const void* part, const void* w, const void* b, float eps, int64_t rows,
+                  int64_t hidden, void* out, void* sum_out) {
+  RB_REQUIRE(rows > 0 && rows <= kTpMaxRows, "exchange_norm: %lld rows exceed the exchange buffer", (long long)rows);
+  RB_REQUIRE((hidden % 8) == 0 && hidden <= 16384, "exchange_norm: hidden %lld unsupported", (long long)hidden);
+  RB_REQUIRE((part != nullptr) != (acc != nullptr && n_acc > 0), "exchange_norm: exactly one form of the partial product");
+  RB_REQUIRE(tp.size >= 1 && tp.size <= kTpMaxRanks && (parity == 0 || parity == 1), "exchange_norm: bad group");
+  using T = __nv_bfloat16;
+  const size_t acc_stride = (size_t)rows * hidden;
+  RB_REQUIRE(aligned16(h) && aligned16(acc) && aligned16(acc_bias) && aligned16(part) && aligned16(w) && aligned16(b) &&
+                 aligned16(out) && aligned16(sum_out) && ((acc_stride * sizeof(float)) % 16) == 0,
+             "exchange_norm: operands must be 16-byte aligned");
+  ProfScope prof(ctx, RB_PROF_NORM, (double)rows * hidden * (2.0 * (3 + 2 * tp.size) + 4.0 * n_acc), 0.0);
+  const int nchunk = (int)(hidden / 8);
+  const int threads = std::min(512, (nchunk + 31) / 32 * 32);
+  const int chunks = (nchunk + threads - 1) / threads;
+  auto go = [&](auto kern) {
+    return launch_kernel(kern, dim3((unsigned)rows), dim3(threads), 0, ctx->stream, ctx->pdl, kind, (const T*)h, acc, n_acc,
+                         acc_stride, (const T*)acc_bias, (const T*)part, (const T*)w, (const T*)b, eps, (int)hidden, (T*)out,
+                         (T*)sum_out, tp, parity, ctx->status_dev, ctx->wait_budget_cycles);
+  };
+  if (chunks == 1) RB_CUDA(go(exchange_norm_kernel<T, 1>));
+  else if (chunks == 2) RB_CUDA(go(exchange_norm_kernel<T, 2>));
+  else RB_CUDA(go(exchange_norm_kernel<T, 4>));
   ctx->launches++;
   return RB_OK;
 }
@@ -710,17 +789,6 @@ int act_from_partials(rb_ctx* ctx, const float* part, int n_split, int64_t rows,
   RB_CUDA(launch_kernel(act_from_partials_kernel, dim3((unsigned)blocks), dim3(128), 0, ctx->stream, ctx->pdl, part, n_split,
                         (size_t)rows * n_all, (int)n_all, (int)n_out, gated ? 1 : 0, (const __nv_bfloat16*)bias, act,
                         (__nv_bfloat16*)out, chunks));
-  ctx->launches++;
-  return RB_OK;
-}
-
-int tp_publish(rb_ctx* ctx, const TpPeers& tp, const float* acc, int n_acc, const void* bias, const void* x, int64_t rows,
-               int64_t hidden) {
-  RB_REQUIRE(rows > 0 && rows <= kTpMaxRows && hidden % 8 == 0, "tp_publish: bad shape");
-  ProfScope prof(ctx, RB_PROF_OTHER, (double)rows * hidden * (2.0 + 4.0 * n_acc), 0.0);
-  const int threads = std::min(512, (int)((hidden / 8 + 31) / 32 * 32));
-  RB_CUDA(launch_kernel(tp_publish_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(threads), 0, ctx->stream, ctx->pdl, acc,
-                        n_acc, (size_t)rows * hidden, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)x, (int)hidden, tp));
   ctx->launches++;
   return RB_OK;
 }

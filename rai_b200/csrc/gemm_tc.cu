@@ -22,12 +22,13 @@
 //            one GPU); `reduce` (M <= 64) sums them inside this kernel - every CTA holds one (tile, split),
 //            all are resident at once, the splits of a tile wait for one another (bounded) and each then
 //            sums one slice of the tile's rows in split order and applies the full epilogue (bias,
-//            activation, gating, residual) to it.  With `push` the finished slice goes into this rank's
-//            place in every tensor-parallel peer's exchange buffer (plain peer stores over NVLink) and the
-//            last CTA raises the flags: the row-parallel GEMM and its share of the allreduce are one kernel.
-//            (Running the splits of a tile as a thread-block cluster that reduces through distributed shared
-//            memory was built and measured: 5 us slower per launch, because a cluster is only scheduled once
-//            all its SMs are free and so loses the overlap with the previous kernel's tail.)
+//            activation, gating, residual) to it.
+//            (Two variants were built, measured and removed: the splits of a tile as a thread-block cluster
+//            reducing through distributed shared memory - 5 us slower per launch, a cluster is only scheduled
+//            once all its SMs are free and so loses the overlap with the previous kernel's tail - and, on top of
+//            `reduce`, an epilogue that pushes the finished slice straight into the tensor-parallel peers'
+//            exchange buffers - 9 us per launch against 8 us for the separate publishing kernel, whose many
+//            small blocks read the slabs with far more parallelism than one CTA per tile slice can.)
 // GATED computes act(X.Wg^T) * (X.Wu^T) with two accumulators per stage (qwen2.rs:100-103).
 //
 // Every barrier wait is bounded; a give-up is recorded in the context's status word and the CTA
@@ -86,10 +87,8 @@ struct Params {
   int reduce;           // split-K reduced inside the kernel: the splits of a tile wait for one another (see the epilogue)
   uint32_t* tile_count; // reduce: arrivals per tile, and readers done per tile; both self-resetting
   uint32_t* tile_done;
-  int push;             // the output goes to the tensor-parallel peers' exchange buffers (see TpPeers)
   long long wait_cycles;  // give-up budget of every bounded wait
   uint32_t* status;
-  TpPeers tp;
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
@@ -518,12 +517,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
         const bool col_ok = gn < p.n;
         const float bias = (!GATED && p.bias && col_ok) ? __bfloat162float(p.bias[gn]) : 0.f;
         const size_t slab = (size_t)p.m * p.n, set = (size_t)ns * slab;
-        uint32_t seq = 0;
-        size_t push_off = 0;
-        if (p.push) {
-          seq = *reinterpret_cast<volatile uint32_t*>(p.tp.seq) + 1u;
-          push_off = ((size_t)(seq & 1u) * p.tp.size + p.tp.rank) * p.tp.slot_elems;
-        }
         for (int jc = j0; jc < j1; jc += 32) {
           const int jc1 = min(j1, jc + 32);
           for (int j = jc; j < jc1; j += 4) {
@@ -563,7 +556,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
               if (j + i < jc1) epi_tile[(j + i - jc) * kEpiPitch + lane_row] = __float2bfloat16_rn(a[i]);
           }
           epi_barrier();
-          // 16-byte pieces of output rows: residual, then the store (to every peer's exchange buffer when pushing)
+          // 16-byte pieces of output rows: residual, then the store
           for (int id = et; id < (jc1 - jc) * (kBM / 8); id += 128) {
             const int jj = id / (kBM / 8), c8 = (id % (kBM / 8)) * 8;
             const int gm = qt * BN + jc + jj, gn8 = pt * kBM + c8;
@@ -578,33 +571,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__
               for (int i = 0; i < 8; ++i) a8[i] += r8[i];
               o = pack8(a8);
             }
-            if (p.push) {
-#pragma unroll
-              for (int r = 0; r < kTpMaxRanks; ++r)
-                if (r < p.tp.size)
-                  *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(const_cast<void*>(p.tp.xbuf[r])) + push_off + at) = o;
-            } else {
-              *reinterpret_cast<uint4*>(p.out + at) = o;
-            }
+            *reinterpret_cast<uint4*>(p.out + at) = o;
           }
-          epi_barrier();  // the staging rows are rewritten by the next chunk; also orders the stores before the fences below
+          epi_barrier();  // the staging rows are rewritten by the next chunk
         }
         if (et == 0) {
           // this CTA has read what it needs of the tile's slabs: the last reader re-arms the counters
           if (atomicAdd(p.tile_done + tile, 1u) == (uint32_t)ns - 1u) { p.tile_count[tile] = 0u; p.tile_done[tile] = 0u; }
-          if (p.push) {
-            // the barrier above orders the epilogue threads' peer stores before this fence; the CTA that is counted
-            // last publishes the sequence number and raises this rank's flag on every peer
-            __threadfence_system();
-            const unsigned int arrived = atomicAdd(p.tp.block_count, 1u);
-            if (arrived == gridDim.x - 1) {
-              *p.tp.block_count = 0u;
-              *reinterpret_cast<volatile uint32_t*>(p.tp.seq) = seq;
-              __threadfence_system();
-              for (int r = 0; r < p.tp.size; ++r)
-                *reinterpret_cast<volatile uint32_t*>(p.tp.flags[r] + (seq & 1u) * kTpMaxRanks + p.tp.rank) = seq;
-            }
-          }
         }
       }
     }
@@ -749,16 +722,13 @@ int gemm_tc_pick_splits(rb_ctx* ctx, int64_t m, int64_t n, int64_t k) {
 
 // Splits of a launch that reduces split-K inside the kernel: enough to fill the SMs, at most 8, at least two K
 // blocks each.  0 = this launch does not take that form.  On one GPU the consumer-side reduction (`partials`) is
-// cheaper, so the form is used where something follows the sum inside the same kernel: a push to tensor-parallel
-// peers, or an epilogue the caller asked for (`reduce`).
+// cheaper, so the form is used only where the caller asks for the whole epilogue in one launch (`reduce`).
 static int reduce_splits(rb_ctx* ctx, const GemmArgs& a, int num_kb, bool gated) {
-  if (!(a.push || a.reduce) || a.partials || a.m > 64 || (a.n % 8) != 0) return 0;
-  if (gated && a.push) return 0;
+  if (!a.reduce || a.partials || a.m > 64 || (a.n % 8) != 0) return 0;
   const int64_t tiles = (a.n + kBM - 1) / kBM;  // M <= 64: one tile along the rows
   if (tiles > ctx->sm_count || tiles > kGemmMaxReduceTiles) return 0;
   int64_t s = std::min<int64_t>(8, ctx->sm_count / tiles);
   s = std::min<int64_t>(s, std::max<int64_t>(1, num_kb / 2));
-  if (a.push) return (int)std::max<int64_t>(1, s);   // pushing always takes this form, even unsplit
   if (tiles * 4 >= (int64_t)ctx->sm_count * 3 || s <= 1) return 0;
   return (int)s;
 }
@@ -798,12 +768,6 @@ int gemm_tc_bf16(rb_ctx* ctx, const GemmArgs& a) {
     p.n_split = s;
   }
   const int rs = swap ? reduce_splits(ctx, a, p.num_kb, gated) : 0;
-  if (a.push) {
-    RB_REQUIRE(rs >= 1, "GEMM: pushing to tensor-parallel peers needs M <= 64, N %% 8 == 0 and at most one tile per SM");
-    RB_REQUIRE((int64_t)a.n == a.push->slot_elems / kTpMaxRows, "GEMM: the pushed width differs from the exchange buffer's");
-    p.push = 1;
-    p.tp = *a.push;
-  }
   if (swap) {
     p.p_rows = (int)a.n; p.q_rows = (int)a.m;
     if (gated) {

@@ -151,7 +151,7 @@ struct Pending {  // terms still to be added to the residual stream
   int n_acc = 0;
   const void* acc_bias = nullptr;
   const void* add = nullptr;
-  bool exchange = false;  // the term sits in the peers' exchange buffers (tensor parallel, decode-sized)
+  bool exchange = false;  // the term is one rank's share: the norm point sums it over the tensor-parallel group
   bool any() const { return (acc && n_acc > 0) || add || exchange; }
 };
 
@@ -185,11 +185,12 @@ struct rb_model {
   // peer-memory exchange for decode-sized allreduces (see TpPeers); xchg_base is this rank's region
   TpPeers peers{};
   void* xchg_base = nullptr;
+  int xchg_index = 0;  // exchanges launched so far in this forward pass (an even number per pass: two per layer)
   void* peer_base[kTpMaxRanks] = {};
   bool use_exchange = false;
-  // RAI_B200_TP_FUSED_PUSH=1: row-parallel GEMMs sum their split-K slabs and push to the peers in their own epilogue
-  // (and sharded gate/up GEMMs apply the gating there).  Off by default: measured slower than the separate
-  // publish / activation kernels, whose many small blocks read the slabs with far more parallelism.
+  // RAI_B200_TP_FUSED_GATE=1: a sharded gate/up GEMM sums its split-K slabs and applies activation and gating in its
+  // own epilogue.  Off by default: measured slower than split-K partials plus the small finishing kernel, whose many
+  // blocks read the slabs with far more parallelism.
   bool fused_push = false;
   // Developer builds only (-DRB_DEBUG_AIDS, a library file of its own): RAI_B200_SHARD_ONLY=1 runs one rank's shard
   // without its peers to time the per-rank kernels; its outputs are not the model's.  Always false otherwise.
@@ -249,8 +250,9 @@ int allreduce(rb_model* m, void* buf, size_t count) {
 // v = h + pending ; h = v ; out = norm(v)   (out may be NULL: only fold the pending terms)
 int norm_point(rb_model* m, Pending& pend, const void* w, const void* b, int64_t rows, void* out) {
   if (!out && !pend.any()) return RB_OK;
-  if (pend.exchange) {
-    RB_TRY(norm_tp(m->ctx, m->peers, norm_kind(m), m->h, w, b, (float)m->cfg.norm_eps, rows, m->cfg.hidden_size, out, m->h));
+  if (pend.exchange) {  // the term is this rank's share of a sum over the group: exchange, fold and normalise at once
+    RB_TRY(exchange_norm(m->ctx, m->peers, m->xchg_index++ & 1, norm_kind(m), m->h, pend.acc, pend.n_acc, pend.acc_bias,
+                         pend.add, w, b, (float)m->cfg.norm_eps, rows, m->cfg.hidden_size, out, m->h));
     pend = Pending();
     return RB_OK;
   }
@@ -283,20 +285,14 @@ int linear_into_residual(rb_model* m, Pending& pend, const void* x, const void* 
   if (m->cfg.tp_size > 1) {
     // this rank's partial product -> tmp, summed over ranks, folded into the residual by the next norm
     if (m->use_exchange && rows <= kTpMaxRows && n == m->cfg.hidden_size) {
-      // decode-sized: the partial product goes into the peers' exchange buffers; the next norm sums them as it reads
-      if (reduce_rows(m, rows) && (n % 8) == 0 && (n + 127) / 128 <= std::min(m->ctx->sm_count, kGemmMaxReduceTiles)) {
-        // the GEMM's own epilogue pushes its tiles and raises the flags: one kernel for product and publish
-        GemmArgs a;
-        a.x = x; a.w = w; a.bias = b; a.m = rows; a.n = n; a.k = k; a.push = &m->peers;
-        ProfScope prof(m->ctx, RB_PROF_GEMM, 2.0 * ((double)n * k + (double)rows * k + (double)rows * n * m->peers.size),
-                       2.0 * rows * n * k);
-        RB_TRY(gemm_tc_bf16(m->ctx, a));
-      } else if (use_partials(m, rows, n, k, &s)) {
+      // decode-sized: the next norm point pushes the partial product into the peers' exchange buffers, waits for
+      // theirs and sums them as it reads
+      if (use_partials(m, rows, n, k, &s)) {
         RB_TRY(rb_linear_partials(m->ctx, x, w, m->scratch, rows, n, k, s));
-        RB_TRY(tp_publish(m->ctx, m->peers, m->scratch, s, b, nullptr, rows, n));
+        pend.acc = m->scratch; pend.n_acc = s; pend.acc_bias = b;
       } else {
         RB_TRY(rb_linear(m->ctx, x, w, b, nullptr, m->tmp, rows, n, k, RB_ACT_NONE, m->cfg.dtype));
-        RB_TRY(tp_publish(m->ctx, m->peers, nullptr, 0, nullptr, m->tmp, rows, n));
+        pend.add = m->tmp;
       }
       pend.exchange = true;
       return RB_OK;
@@ -382,6 +378,7 @@ int forward_body(rb_model* m, const uint32_t* tokens, int batch, int seq, void* 
              "forward: this is rank %d of a %d-way tensor-parallel model and rb_model_tp_init has not run", c.tp_rank, c.tp_size);
   const int64_t rows = (int64_t)batch * seq;
   const int H = c.hidden_size, d = m->d;
+  m->xchg_index = 0;
 
   const float emb_scale = c.arch == RB_ARCH_GEMMA ? sqrtf((float)H) : 1.0f;  // gemma.rs:379
   RB_TRY(rb_embed_gather(ctx, m->embed, c.dtype, c.vocab_size, H, tokens, rows, emb_scale, m->h));
@@ -498,11 +495,11 @@ extern "C" int32_t rb_model_tp_init(rb_model* m, const void* id, int32_t id_byte
   RB_NCCL(nccl().CommInitRank(&m->comm, m->cfg.tp_size, u, m->cfg.tp_rank));
   const char* xe = getenv("RAI_B200_TP_EXCHANGE");  // RAI_B200_TP_EXCHANGE=0: NCCL allreduce for every size
   if (m->cfg.dtype != RB_BF16 || m->cfg.tp_size > kTpMaxRanks || (xe && xe[0] == '0') || (m->cfg.hidden_size % 8)) return RB_OK;
-  // ---- peer-memory exchange: one region per rank = [flags 2 x 8 | seq | block_count | pad to 256 B | 2 slots]
+  // ---- peer-memory exchange: one region per rank = [flags: 2 slots x 8 source ranks x 256 rows | 2 data slots]
   rb_ctx* ctx = m->ctx;
   const int tp = m->cfg.tp_size, rank = m->cfg.tp_rank;
   const size_t slot_elems = (size_t)kTpMaxRows * m->cfg.hidden_size;
-  const size_t bytes = 256 + 2 * (size_t)tp * slot_elems * 2;  // header, then [2 slots][tp sources][rows x hidden] bf16
+  const size_t bytes = kTpFlagBytes + 2 * (size_t)tp * slot_elems * 2;  // flags, then [2 slots][tp sources][rows x hidden] bf16
   RB_TRY(rb_malloc(ctx, bytes, &m->xchg_base));
   m->owned.push_back(m->xchg_base);
   RB_CUDA(cudaMemsetAsync(m->xchg_base, 0, bytes, ctx->stream));
@@ -548,15 +545,14 @@ extern "C" int32_t rb_model_tp_init(rb_model* m, const void* id, int32_t id_byte
   TpPeers& p = m->peers;
   for (int r = 0; r < tp; ++r) {
     p.flags[r] = (uint32_t*)m->peer_base[r];
-    p.xbuf[r] = (const char*)m->peer_base[r] + 256;
+    p.xbuf[r] = (const char*)m->peer_base[r] + kTpFlagBytes;
   }
-  // sequence number and arrival counter are touched by this GPU only: keep them off the line the peers write
+  // the two exchange counters are touched by this GPU only: keep them off the lines the peers write
   void* local = nullptr;
   RB_TRY(rb_malloc(ctx, 256, &local));
   m->owned.push_back(local);
   RB_CUDA(cudaMemsetAsync(local, 0, 256, ctx->stream));
   p.seq = (uint32_t*)local;
-  p.block_count = p.seq + 32;
   p.rank = rank; p.size = tp; p.slot_elems = (int64_t)slot_elems;
   // (the vote above was also the meeting point: no rank publishes before every rank has zeroed its region and
   // opened its peers)
@@ -590,7 +586,7 @@ extern "C" int32_t rb_model_create(rb_ctx* ctx, const rb_model_config* cfg, rb_m
   {
     const char* g = getenv("RAI_B200_GRAPH");  // RAI_B200_GRAPH=0: plain launches for every decode step
     m->use_graph = !(g && g[0] == '0');
-    const char* fp = getenv("RAI_B200_TP_FUSED_PUSH");
+    const char* fp = getenv("RAI_B200_TP_FUSED_GATE");
     m->fused_push = fp && fp[0] == '1';
   }
   m->d = c.hidden_size / nq;
@@ -767,13 +763,12 @@ extern "C" int32_t rb_model_create(rb_ctx* ctx, const rb_model_config* cfg, rb_m
     if (m->shard_only && c.dtype == RB_BF16 && (H % 8) == 0) {
       // the exchange kernels still run, against a group of one (this rank's own region)
       const size_t slot_elems = (size_t)kTpMaxRows * H;
-      st = dev_alloc(m, 512 + 2 * slot_elems * 2, &m->xchg_base, true);
+      st = dev_alloc(m, kTpFlagBytes + 512 + 2 * slot_elems * 2, &m->xchg_base, true);
       if (st != RB_OK) { rb_model_destroy(m); return st; }
       TpPeers& p = m->peers;
       p.flags[0] = (uint32_t*)m->xchg_base;
-      p.seq = (uint32_t*)m->xchg_base + 64;
-      p.block_count = p.seq + 32;
-      p.xbuf[0] = (const char*)m->xchg_base + 512;
+      p.seq = (uint32_t*)((char*)m->xchg_base + kTpFlagBytes);
+      p.xbuf[0] = (const char*)m->xchg_base + kTpFlagBytes + 512;
       p.rank = 0; p.size = 1; p.slot_elems = (int64_t)slot_elems;
       m->peer_base[0] = m->xchg_base;
       m->use_exchange = true;

@@ -66,55 +66,62 @@ extern "C" int32_t rb_selftest_wait_gives_up(rb_ctx* ctx, int32_t which, int64_t
                   returned, w[0], w[1]);
     return RB_OK;
   }
-  // ---- the tensor-parallel norm over a two-member group that lives entirely in this GPU's memory
+  // ---- the tensor-parallel exchange over a two-member group that lives entirely in this GPU's memory; this launch
+  // plays member 0 and nobody plays member 1
   const int rows = 2, hidden = 256;
-  DevBuf region, x, wt, out, sum;
+  DevBuf region, part, h, wt, out, sum;
   const size_t slot_elems = (size_t)kTpMaxRows * hidden;
-  const size_t region_bytes = 512 + 2 * 2 * slot_elems * 2;
+  const size_t region_bytes = kTpFlagBytes + 512 + 2 * 2 * slot_elems * 2;   // flags | counters | 2 slots x 2 sources
+  const size_t act_bytes = (size_t)rows * hidden * 2;
   RB_CUDA(cudaMalloc(&region.p, region_bytes));
-  RB_CUDA(cudaMalloc(&x.p, (size_t)rows * hidden * 2));
+  RB_CUDA(cudaMalloc(&part.p, act_bytes));
+  RB_CUDA(cudaMalloc(&h.p, act_bytes));
   RB_CUDA(cudaMalloc(&wt.p, (size_t)hidden * 2));
-  RB_CUDA(cudaMalloc(&out.p, (size_t)rows * hidden * 2));
-  RB_CUDA(cudaMalloc(&sum.p, (size_t)rows * hidden * 2));
+  RB_CUDA(cudaMalloc(&out.p, act_bytes));
+  RB_CUDA(cudaMalloc(&sum.p, act_bytes));
   RB_CUDA(cudaMemsetAsync(region.p, 0, region_bytes, ctx->stream));
-  RB_CUDA(cudaMemsetAsync(x.p, 0, (size_t)rows * hidden * 2, ctx->stream));
-  std::vector<uint16_t> ones((size_t)hidden, 0x3F80u);  // bf16 1.0
+  RB_CUDA(cudaMemsetAsync(h.p, 0, act_bytes, ctx->stream));
+  std::vector<uint16_t> ones((size_t)rows * hidden, 0x3F80u);  // bf16 1.0
   RB_CUDA(cudaMemcpyAsync(wt.p, ones.data(), (size_t)hidden * 2, cudaMemcpyHostToDevice, ctx->stream));
-  RB_CUDA(cudaMemsetAsync(out.p, 0x5A, (size_t)rows * hidden * 2, ctx->stream));
-  RB_CUDA(cudaMemsetAsync(sum.p, 0x5A, (size_t)rows * hidden * 2, ctx->stream));
+  RB_CUDA(cudaMemcpyAsync(part.p, ones.data(), act_bytes, cudaMemcpyHostToDevice, ctx->stream));
+  RB_CUDA(cudaMemsetAsync(out.p, 0x5A, act_bytes, ctx->stream));
+  RB_CUDA(cudaMemsetAsync(sum.p, 0x5A, act_bytes, ctx->stream));
   TpPeers tp{};
-  uint32_t* flags = (uint32_t*)region.p;          // [2 slots][kTpMaxRanks]
+  uint32_t* flags = (uint32_t*)region.p;          // [2 slots][kTpMaxRanks][kTpMaxRows]
   tp.flags[0] = tp.flags[1] = flags;
-  tp.xbuf[0] = tp.xbuf[1] = (const char*)region.p + 512;
-  tp.seq = flags + 64;                             // exchange number 1 has been "published" by member 0 only
-  tp.block_count = flags + 96;
+  tp.seq = (uint32_t*)((char*)region.p + kTpFlagBytes);
+  tp.xbuf[0] = tp.xbuf[1] = (const char*)region.p + kTpFlagBytes + 512;
   tp.rank = 0; tp.size = 2; tp.slot_elems = (int64_t)slot_elems;
-  const uint32_t one = 1u;
-  RB_CUDA(cudaMemcpyAsync(tp.seq, &one, sizeof(one), cudaMemcpyHostToDevice, ctx->stream));
-  RB_CUDA(cudaMemcpyAsync(flags + 1 * kTpMaxRanks + 0, &one, sizeof(one), cudaMemcpyHostToDevice, ctx->stream));
-  RB_CUDA(cudaStreamSynchronize(ctx->stream));  // `ones` and `one` are read by the copies above
+  RB_CUDA(cudaStreamSynchronize(ctx->stream));  // the host buffers above are read by the copies
   const long long keep = ctx->wait_budget_cycles;
   ctx->wait_budget_cycles = budget;
-  int st = norm_tp(ctx, tp, RB_NORM_RMS, x.p, wt.p, nullptr, 1e-6f, rows, hidden, out.p, sum.p);
+  // exchange number 1 (parity 0): member 1 never raises its flags
+  int st = exchange_norm(ctx, tp, 0, RB_NORM_RMS, h.p, nullptr, 0, nullptr, part.p, wt.p, nullptr, 1e-6f, rows, hidden, out.p, sum.p);
   ctx->wait_budget_cycles = keep;
   RB_TRY(st);
   RB_TRY(read_status(ctx, w));
-  std::vector<uint16_t> got((size_t)rows * hidden);
-  RB_CUDA(cudaMemcpy(got.data(), out.p, got.size() * 2, cudaMemcpyDeviceToHost));
+  std::vector<uint16_t> got((size_t)rows * hidden), got_sum((size_t)rows * hidden);
+  RB_CUDA(cudaMemcpy(got.data(), out.p, act_bytes, cudaMemcpyDeviceToHost));
+  RB_CUDA(cudaMemcpy(got_sum.data(), sum.p, act_bytes, cudaMemcpyDeviceToHost));
   bool untouched = true;
   for (uint16_t v : got) untouched = untouched && v == 0x5A5Au;
+  for (uint16_t v : got_sum) untouched = untouched && v == 0x5A5Au;
   if (w[0] != (uint32_t)(-RB_ERR_TIMEOUT) || w[1] != 0x7A11u || !untouched)
     return fail(RB_ERR_CUDA, "exchange-wait self-test: expected a give-up at 0x7A11 with the outputs untouched, got status={%u, 0x%x}, "
                 "outputs %s", w[0], w[1], untouched ? "untouched" : "written");
-  // the same call once the second member has raised its flag: completes, nothing recorded
-  RB_CUDA(cudaMemcpy(flags + 1 * kTpMaxRanks + 1, &one, sizeof(one), cudaMemcpyHostToDevice));
-  RB_TRY(norm_tp(ctx, tp, RB_NORM_RMS, x.p, wt.p, nullptr, 1e-6f, rows, hidden, out.p, sum.p));
+  // exchange number 2 (parity 1, slot 0) with member 1's rows "arrived" (all zero) and its flags raised: completes,
+  // nothing recorded, and the sum is member 0's term alone
+  const uint32_t twos[2] = {2u, 2u};
+  RB_CUDA(cudaMemcpy(flags + ((size_t)0 * kTpMaxRanks + 1) * kTpMaxRows, twos, sizeof(twos), cudaMemcpyHostToDevice));
+  RB_TRY(exchange_norm(ctx, tp, 1, RB_NORM_RMS, h.p, nullptr, 0, nullptr, part.p, wt.p, nullptr, 1e-6f, rows, hidden, out.p, sum.p));
   RB_TRY(read_status(ctx, w));
-  RB_CUDA(cudaMemcpy(got.data(), out.p, got.size() * 2, cudaMemcpyDeviceToHost));
+  RB_CUDA(cudaMemcpy(got.data(), out.p, act_bytes, cudaMemcpyDeviceToHost));
+  RB_CUDA(cudaMemcpy(got_sum.data(), sum.p, act_bytes, cudaMemcpyDeviceToHost));
   bool written = true;
-  for (uint16_t v : got) written = written && v == 0u;  // norm of an all-zero row is zero
+  for (uint16_t v : got) written = written && v == 0x3F80u;      // an all-ones row, RMS-normalised with unit weights
+  for (uint16_t v : got_sum) written = written && v == 0x3F80u;  // 0 + (1 + 0)
   if (w[0] != 0u || !written)
     return fail(RB_ERR_CUDA, "exchange-wait self-test: the healthy call after the give-up failed (status %u, outputs %s)", w[0],
-                written ? "written" : "not written");
+                written ? "as expected" : "wrong");
   return RB_OK;
 }

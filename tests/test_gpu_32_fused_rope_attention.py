@@ -1,6 +1,10 @@
 """The single-token step as one kernel (rb_rope_attention_decode) against the two separate calls it replaces
 (rb_rope_kv_append then rb_attention): attention output and the appended K/V rows must be identical bit for
-bit, for every input form (bf16 rows, float32 split-K partials, bias), group size, page boundary and KV split."""
+bit, for every input form (bf16 rows, float32 split-K partials, bias), group size, page boundary and KV split.
+
+This is a bit-identity check between two entry points of the same library, not a parity check: the separate path is
+held to the CPU oracle by test_gpu_30_attention.py, the fused path by the model tests (every decode step they run goes
+through it) and, at the benchmark's shape, by test_gpu_33_attention_bench_shapes.py."""
 import ctypes
 import math
 
