@@ -88,8 +88,10 @@ const char* rb_last_error(void);
 /* Copies the 4-word device status record {code, where, detail0, detail1} to `out4` (synchronises). */
 int32_t rb_status_word(rb_ctx* ctx, uint32_t* out4);
 int32_t rb_sm_count(rb_ctx* ctx);
-/* How long a device-side wait (on a copy, a tensor-core result or a tensor-parallel peer) may last before the
- * kernel gives up, reports RB_ERR_TIMEOUT through the status word and returns.  Default: about one second.
+/* How long a device-side wait for a tensor-parallel peer may last before the kernel gives up, reports
+ * RB_ERR_TIMEOUT through the status word and returns; waits inside one kernel (on a copy, a tensor-core result, a
+ * sibling block) get four times as long, so that a missing peer is reported by the exchange that waited for it and
+ * not by a kernel queued behind it.  Default: about one second.
  * Stands in for nothing in the reference, whose only device code is candle's; it is the knob behind the
  * "never blocks without bound" convention above.  Applies to launches made after the call. */
 int32_t rb_set_wait_budget_us(rb_ctx* ctx, int64_t microseconds);

@@ -727,7 +727,7 @@ int attention_mma_bf16(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, in
   p.out = (bf16*)out;
   p.status = ctx->status_dev;
   p.window = c->window;
-  p.wait_cycles = ctx->wait_budget_cycles;
+  p.wait_cycles = ctx->local_wait_cycles();
   RB_REQUIRE(p.group >= 1 && p.group <= 16 && q_heads % c->kv_heads == 0,
              "attention: %d query heads per KV head unsupported (1..16)", p.group);
   // prefill with at least one 128-row query tile and head size 64 or 128: the tcgen05 kernel
@@ -777,7 +777,7 @@ int attention_decode_fused_rope(rb_ctx* ctx, const void* qkv, const float* acc, 
   p.out = (bf16*)out;
   p.status = ctx->status_dev;
   p.window = c->window;
-  p.wait_cycles = ctx->wait_budget_cycles;
+  p.wait_cycles = ctx->local_wait_cycles();
   p.fuse = 1;
   p.f_qkv = (const bf16*)qkv;
   p.f_acc = n_acc > 0 ? acc : nullptr;
@@ -850,7 +850,7 @@ extern "C" int32_t rb_attention_decode_static(rb_ctx* ctx, const void* q, rb_kv_
   p.out = (bf16*)out;
   p.status = ctx->status_dev;
   p.window = c->window;
-  p.wait_cycles = ctx->wait_budget_cycles;
+  p.wait_cycles = ctx->local_wait_cycles();
   switch (c->head_dim) {
     case 64: return launch_attention_decode_static<64>(ctx, c, p, batch, max_len, scratch);
     case 80: return launch_attention_decode_static<80>(ctx, c, p, batch, max_len, scratch);

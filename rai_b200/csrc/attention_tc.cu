@@ -405,7 +405,7 @@ int launch_tc(rb_ctx* ctx, const void* q, rb_kv_cache* c, int layer, int batch, 
   p.scale_log2 = scale * kLog2e;
   p.out = (bf16*)out;
   p.status = ctx->status_dev;
-  p.wait_cycles = ctx->wait_budget_cycles;
+  p.wait_cycles = ctx->local_wait_cycles();
   dim3 grid((unsigned)((s_new + kBM - 1) / kBM), (unsigned)q_heads, (unsigned)batch);
 #ifdef RB_DEBUG_AIDS
   static const bool trace = getenv("RAI_B200_ATTN_TRACE") != nullptr;

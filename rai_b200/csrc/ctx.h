@@ -26,7 +26,11 @@ struct rb_ctx {
   float* gemm_scratch = nullptr;   // float32 slabs of the GEMMs that reduce split-K inside the kernel; grow-only
   size_t gemm_scratch_bytes = 0;
   uint32_t* gemm_tile_count = nullptr;  // [2][kGemmMaxReduceTiles] arrival / done counters of those GEMMs, self-resetting
-  long long wait_budget_cycles = 2000000000LL;  // give-up time of every bounded device-side wait (rb_set_wait_budget_us)
+  long long wait_budget_cycles = 2000000000LL;  // give-up time of a device-side wait for ANOTHER GPU (rb_set_wait_budget_us)
+  // Waits inside one kernel (operand rings, accumulators, sibling blocks) may begin before the kernel's predecessor
+  // has finished, and that predecessor may itself be waiting for a peer: they get four times the budget, so that
+  // when a peer never arrives it is the exchange that reports it, not a bystander further down the stream.
+  long long local_wait_cycles() const { return wait_budget_cycles > (1LL << 60) ? wait_budget_cycles : 4 * wait_budget_cycles; }
   int tmap_cache_limit = 4096;  // tensor maps kept before the cache is emptied
   // argmax across blocks: running best (key << 32 | index) and arrival count per row; self-resetting
   unsigned long long* argmax_best = nullptr;

@@ -646,7 +646,7 @@ int launch(rb_ctx* ctx, const GemmArgs& a, Params& p, int want_split = 0) {
   if (SWAP) stages = std::max(2, std::min(C::kStages, (int)(ctx->gemm_ring_bytes / C::kStageBytes)));
   p.stages = stages;
   const size_t smem = (size_t)stages * C::kStageBytes + 1024;
-  p.wait_cycles = ctx->wait_budget_cycles;
+  p.wait_cycles = ctx->local_wait_cycles();
 
   if (SWAP && want_split >= 1) {
     // Split-K reduced inside the kernel: one CTA per (tile, split), all resident at once.
