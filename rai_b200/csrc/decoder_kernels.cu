@@ -129,7 +129,9 @@ __device__ __forceinline__ void add8_bf16(const uint4& u, float* v) {
   for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] += f.x; v[2 * i + 1] += f.y; }
 }
 
-template <typename T, int kChunks>
+// kSlabs = false is the instantiation for calls without split-K partials (prefill): without the registers that keep
+// eight slab loads in flight, several blocks share an SM and the kernel streams at memory speed.
+template <typename T, int kChunks, bool kSlabs>
 __global__ void __launch_bounds__(512) norm_vec_kernel(int kind, const T* __restrict__ x, const T* __restrict__ add,
                                 const float* __restrict__ acc, int n_acc, size_t acc_stride,
                                 const T* __restrict__ acc_bias, const T* __restrict__ w, const T* __restrict__ b,
@@ -170,10 +172,12 @@ __global__ void __launch_bounds__(512) norm_vec_kernel(int kind, const T* __rest
     if (add) { load8(add + base + ch * 8, t);
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[c][i] += t[i]; }
-    add_slabs(acc, n_acc, acc_stride, base + ch * 8, v[c]);
-    if (acc_bias) { load8(acc_bias + ch * 8, t);
+    if (kSlabs) {
+      add_slabs(acc, n_acc, acc_stride, base + ch * 8, v[c]);
+      if (acc_bias) { load8(acc_bias + ch * 8, t);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[c][i] += t[i]; }
+        for (int i = 0; i < 8; ++i) v[c][i] += t[i]; }
+    }
     round_to<T>(v[c]);  // the residual stream is stored in the model dtype
     if (sum_out) store8(sum_out + base + ch * 8, v[c]);
 #pragma unroll
@@ -704,15 +708,21 @@ static int norm_launch(rb_ctx* ctx, int kind, const void* x, const void* add, co
     int threads = std::min(512, (nchunk + 31) / 32 * 32);
     const int chunks = (nchunk + threads - 1) / threads;
     // decode-sized calls get a block per row (pure latency); prefill-sized ones a few blocks per SM that walk the rows
-    const int64_t blocks = std::min<int64_t>(rows, (int64_t)ctx->sm_count * 4);
+    const int64_t blocks = std::min<int64_t>(rows, (int64_t)ctx->sm_count * 8);
     auto go = [&](auto kern) {
       return launch_kernel(kern, dim3((unsigned)blocks), dim3(threads), 0, ctx->stream, ctx->pdl, kind, (const T*)x,
                            (const T*)add, acc, n_acc, acc_stride, (const T*)acc_bias, (const T*)w, (const T*)b, eps,
                            (int)hidden, (T*)out, (T*)sum_out, (int64_t)rows);
     };
-    if (chunks == 1) RB_CUDA(go(norm_vec_kernel<T, 1>));
-    else if (chunks == 2) RB_CUDA(go(norm_vec_kernel<T, 2>));
-    else RB_CUDA(go(norm_vec_kernel<T, 4>));
+    if (n_acc > 0 || acc_bias) {
+      if (chunks == 1) RB_CUDA(go(norm_vec_kernel<T, 1, true>));
+      else if (chunks == 2) RB_CUDA(go(norm_vec_kernel<T, 2, true>));
+      else RB_CUDA(go(norm_vec_kernel<T, 4, true>));
+    } else {
+      if (chunks == 1) RB_CUDA(go(norm_vec_kernel<T, 1, false>));
+      else if (chunks == 2) RB_CUDA(go(norm_vec_kernel<T, 2, false>));
+      else RB_CUDA(go(norm_vec_kernel<T, 4, false>));
+    }
     return RB_OK;
   }
   const size_t smem = (size_t)hidden * sizeof(float);
