@@ -263,6 +263,9 @@ __global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* _
   const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(tp.seq + parity * 32) + 1u;
   const size_t slot_off = (size_t)(seq & 1u) * tp.size * tp.slot_elems;   // [2 slots][size sources][rows x hidden]
   // ---- this rank's partial row, rounded to the model dtype, into every rank's buffer
+  uint4 own[kChunks];
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) own[c] = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
   for (int c = 0; c < kChunks; ++c) {
     const int ch = threadIdx.x + c * blockDim.x;
@@ -276,20 +279,21 @@ __global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* _
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[i] += t[i]; }
     const uint4 packed = pack8_bf16(v);
+    own[c] = packed;
 #pragma unroll
     for (int r = 0; r < kTpMaxRanks; ++r)
       if (r < tp.size)
         *reinterpret_cast<uint4*>(reinterpret_cast<T*>(const_cast<void*>(tp.xbuf[r])) + slot_off + (size_t)tp.rank * tp.slot_elems +
                                   base + ch * 8) = packed;
   }
-  __syncthreads();  // the block's stores are ordered before the fences below (cumulativity through the barrier)
+  __syncthreads();  // the block's stores are ordered before the releases below (cumulativity through the barrier)
   if ((int)threadIdx.x < tp.size) {
-    __threadfence_system();  // this row is performed at every peer before its flag can be seen there
+    if (!(tp.lean & 1)) __threadfence_system();  // this row is performed at every peer before its flag can be seen there
     st_release_sys(tp.flags[threadIdx.x] + ((size_t)(seq & 1u) * kTpMaxRanks + tp.rank) * kTpMaxRows + row, seq);
     // ---- and the same row from every rank: thread t waits for rank t
     const uint32_t* flag = tp.flags[tp.rank] + ((size_t)(seq & 1u) * kTpMaxRanks + threadIdx.x) * kTpMaxRows + row;
     const long long t0 = clock64();
-    while ((int32_t)(ld_acquire_sys(flag) - seq) < 0) {
+    while (!((tp.lean & 2) && (int)threadIdx.x == tp.rank) && (int32_t)(ld_acquire_sys(flag) - seq) < 0) {
       if (clock64() - t0 > wait_cycles) {
         status[0] = (uint32_t)(-RB_ERR_TIMEOUT); status[1] = 0x7A11u; status[2] = (uint32_t)tp.rank; status[3] = seq;
         give_up = 1u;
@@ -316,7 +320,7 @@ __global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* _
     float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int r = 0; r < kTpMaxRanks; ++r)
-      if (r < tp.size) pr[r] = load16_sys(mine + (size_t)r * tp.slot_elems + ch * 8);
+      if (r < tp.size) pr[r] = ((tp.lean & 2) && r == tp.rank) ? own[c] : load16_sys(mine + (size_t)r * tp.slot_elems + ch * 8);
     if (h) load8(h + base + ch * 8, v[c]);
 #pragma unroll
     for (int r = 0; r < kTpMaxRanks; ++r)   // rank order, on every rank alike
