@@ -85,7 +85,6 @@ struct TpPeers {
   uint32_t* flags[kTpMaxRanks];    // every rank's flag array, [2][kTpMaxRanks][kTpMaxRows]
   uint32_t* seq;                   // local: two exchange counters 128 bytes apart, seq[0] for even launches, seq[32] for odd
   int rank, size;
-  int lean;                        // experiment switch
   int64_t slot_elems;              // kTpMaxRows * hidden
 };
 

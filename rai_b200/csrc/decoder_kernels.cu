@@ -226,10 +226,10 @@ __global__ void __launch_bounds__(512) norm_vec_kernel(int kind, const T* __rest
 
 // Tensor-parallel allreduce of a row-parallel product, fused with the residual add and the norm that follow it.  One
 // block per row: it finishes this rank's partial row (split-K slabs + bias, or a bf16 tensor), pushes it into this
-// rank's place of the next slot in EVERY rank's exchange buffer (posted stores over NVLink, nobody waits for a reply),
-// raises that row's flag on every peer, then waits (bounded) for the same row from every rank, sums the copies that
-// now sit in its OWN memory in rank order - the same on every rank - adds the residual stream and normalises.  A row
-// waits only for that row: no block waits for another block of its own kernel.
+// rank's place of the next slot in every PEER's exchange buffer (posted stores over NVLink, nobody waits for a reply),
+// raises that row's flag on every peer, then waits (bounded) for the same row from every peer, sums the copies that
+// now sit in its OWN memory - and its own, still in registers - in rank order, the same on every rank, adds the
+// residual stream and normalises.  A row waits only for that row: no block waits for another block of its own kernel.
 //
 // Exchange numbers live on the device so that a captured graph replays unchanged: a launch with parity q reads
 // counter[q] (exchange number = counter[q] + 1) and, when done, sets counter[q ^ 1] to that number for the next
@@ -282,18 +282,20 @@ __global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* _
     own[c] = packed;
 #pragma unroll
     for (int r = 0; r < kTpMaxRanks; ++r)
-      if (r < tp.size)
+      if (r < tp.size && r != tp.rank)
         *reinterpret_cast<uint4*>(reinterpret_cast<T*>(const_cast<void*>(tp.xbuf[r])) + slot_off + (size_t)tp.rank * tp.slot_elems +
                                   base + ch * 8) = packed;
   }
   __syncthreads();  // the block's stores are ordered before the releases below (cumulativity through the barrier)
   if ((int)threadIdx.x < tp.size) {
-    if (!(tp.lean & 1)) __threadfence_system();  // this row is performed at every peer before its flag can be seen there
-    st_release_sys(tp.flags[threadIdx.x] + ((size_t)(seq & 1u) * kTpMaxRanks + tp.rank) * kTpMaxRows + row, seq);
-    // ---- and the same row from every rank: thread t waits for rank t
+    // a release at system scope: every store of the block that the barrier ordered before it is performed at the peer
+    // before the flag can be seen there (no separate fence: the release carries one)
+    if ((int)threadIdx.x != tp.rank)
+      st_release_sys(tp.flags[threadIdx.x] + ((size_t)(seq & 1u) * kTpMaxRanks + tp.rank) * kTpMaxRows + row, seq);
+    // ---- and the same row from every other rank: thread t waits for rank t (this rank's own row is still in registers)
     const uint32_t* flag = tp.flags[tp.rank] + ((size_t)(seq & 1u) * kTpMaxRanks + threadIdx.x) * kTpMaxRows + row;
     const long long t0 = clock64();
-    while (!((tp.lean & 2) && (int)threadIdx.x == tp.rank) && (int32_t)(ld_acquire_sys(flag) - seq) < 0) {
+    while ((int)threadIdx.x != tp.rank && (int32_t)(ld_acquire_sys(flag) - seq) < 0) {
       if (clock64() - t0 > wait_cycles) {
         status[0] = (uint32_t)(-RB_ERR_TIMEOUT); status[1] = 0x7A11u; status[2] = (uint32_t)tp.rank; status[3] = seq;
         give_up = 1u;
@@ -320,7 +322,7 @@ __global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* _
     float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int r = 0; r < kTpMaxRanks; ++r)
-      if (r < tp.size) pr[r] = ((tp.lean & 2) && r == tp.rank) ? own[c] : load16_sys(mine + (size_t)r * tp.slot_elems + ch * 8);
+      if (r < tp.size) pr[r] = r == tp.rank ? own[c] : load16_sys(mine + (size_t)r * tp.slot_elems + ch * 8);
     if (h) load8(h + base + ch * 8, v[c]);
 #pragma unroll
     for (int r = 0; r < kTpMaxRanks; ++r)   // rank order, on every rank alike

@@ -554,7 +554,6 @@ extern "C" int32_t rb_model_tp_init(rb_model* m, const void* id, int32_t id_byte
   RB_CUDA(cudaMemsetAsync(local, 0, 256, ctx->stream));
   p.seq = (uint32_t*)local;
   p.rank = rank; p.size = tp; p.slot_elems = (int64_t)slot_elems;
-  p.lean = getenv("RAI_B200_TP_LEAN") ? atoi(getenv("RAI_B200_TP_LEAN")) : 0;
   // (the vote above was also the meeting point: no rank publishes before every rank has zeroed its region and
   // opened its peers)
   RB_CUDA(cudaStreamSynchronize(ctx->stream));
@@ -771,7 +770,6 @@ extern "C" int32_t rb_model_create(rb_ctx* ctx, const rb_model_config* cfg, rb_m
       p.seq = (uint32_t*)((char*)m->xchg_base + kTpFlagBytes);
       p.xbuf[0] = (const char*)m->xchg_base + kTpFlagBytes + 512;
       p.rank = 0; p.size = 1; p.slot_elems = (int64_t)slot_elems;
-      p.lean = getenv("RAI_B200_TP_LEAN") ? atoi(getenv("RAI_B200_TP_LEAN")) : 0;
       m->peer_base[0] = m->xchg_base;
       m->use_exchange = true;
     }
