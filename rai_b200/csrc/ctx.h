@@ -22,7 +22,7 @@ struct rb_ctx {
   // shared memory a decode-sized GEMM spends on its operand ring (RAI_B200_GEMM_RING_KB overrides)
   size_t gemm_ring_bytes = 200 * 1024;
   bool attn_tc = true;        // RAI_B200_ATTN_TC=0: prefill attention on the mma.sync kernel for every head size (debugging aid)
-  bool gemm_reduce = true;    // RAI_B200_GEMM_REDUCE=0: tensor-parallel GEMMs leave split-K to separate kernels (debugging aid)
+  bool gemm_reduce = true;    // RAI_B200_GEMM_REDUCE=0: rb_linear / rb_gated_linear never split K inside the kernel (debugging aid)
   float* gemm_scratch = nullptr;   // float32 slabs of the GEMMs that reduce split-K inside the kernel; grow-only
   size_t gemm_scratch_bytes = 0;
   uint32_t* gemm_tile_count = nullptr;  // [2][kGemmMaxReduceTiles] arrival / done counters of those GEMMs, self-resetting

@@ -191,7 +191,7 @@ struct rb_model {
   // RAI_B200_TP_FUSED_GATE=1: a sharded gate/up GEMM sums its split-K slabs and applies activation and gating in its
   // own epilogue.  Off by default: measured slower than split-K partials plus the small finishing kernel, whose many
   // blocks read the slabs with far more parallelism.
-  bool fused_push = false;
+  bool fused_gate = false;
   // Developer builds only (-DRB_DEBUG_AIDS, a library file of its own): RAI_B200_SHARD_ONLY=1 runs one rank's shard
   // without its peers to time the per-rank kernels; its outputs are not the model's.  Always false otherwise.
   bool shard_only = false;
@@ -263,9 +263,9 @@ int norm_point(rb_model* m, Pending& pend, const void* w, const void* b, int64_t
 }
 
 // Rows few enough for the GEMM form that sums its split-K slabs inside the kernel and applies the whole epilogue
-// there (used where something must follow the sum at once: the push to tensor-parallel peers, the gating product).
+// there (used where something must follow the sum at once: the gating product of a sharded gate/up).
 bool reduce_rows(const rb_model* m, int64_t rows) {
-  return m->fused_push && m->cfg.dtype == RB_BF16 && rows <= 64 && m->ctx->gemm_reduce && !m->ctx->debug_simple_gemm;
+  return m->fused_gate && m->cfg.dtype == RB_BF16 && rows <= 64 && m->ctx->gemm_reduce && !m->ctx->debug_simple_gemm;
 }
 
 bool use_partials(rb_model* m, int64_t rows, int64_t n, int64_t k, int* splits) {
@@ -587,7 +587,7 @@ extern "C" int32_t rb_model_create(rb_ctx* ctx, const rb_model_config* cfg, rb_m
     const char* g = getenv("RAI_B200_GRAPH");  // RAI_B200_GRAPH=0: plain launches for every decode step
     m->use_graph = !(g && g[0] == '0');
     const char* fp = getenv("RAI_B200_TP_FUSED_GATE");
-    m->fused_push = fp && fp[0] == '1';
+    m->fused_gate = fp && fp[0] == '1';
   }
   m->d = c.hidden_size / nq;
   m->es = dtype_size(c.dtype);
