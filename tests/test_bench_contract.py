@@ -47,3 +47,24 @@ def test_single_rank_passes_of_the_gpu_arm_are_not_collective():
     assert len(calls) == 1
     guard = src.rfind("if ", 0, calls[0])
     assert "world == 1" in src[guard:calls[0]], "the timeline pass must be limited to single-GPU runs"
+
+
+def test_every_committed_profile_names_a_safe_reproducible_command():
+    """Each summary under profiles/ gives the command that made it; every ncu command among them leaves the clocks
+    alone, runs a committed file, and asks for whole sections only on the reduced (2-layer) case."""
+    import glob
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    files = sorted(glob.glob(os.path.join(root, "profiles", "*.md")))
+    assert files, "no profile summaries committed"
+    for path in files:
+        text = open(path).read()
+        commands = re.findall(r"```\n(.*?)\n```", text, flags=re.S)
+        assert commands, f"{os.path.basename(path)} does not say how it was made"
+        for cmd in commands:
+            assert "bench.py" in cmd, f"{os.path.basename(path)}: the command runs something other than the bench"
+            if cmd.lstrip().startswith("ncu"):
+                assert "--clock-control none" in cmd, f"{os.path.basename(path)}: ncu would lock the clocks"
+                if "--set full" in cmd or "--section" in cmd:
+                    assert "--layers 2" in cmd and re.search(r"-c [1-4]\b", cmd), \
+                        f"{os.path.basename(path)}: a multi-pass capture must stay on the small case, a few launches"
