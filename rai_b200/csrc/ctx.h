@@ -79,12 +79,15 @@ constexpr int kGemmMaxReduceTiles = 256;
 
 constexpr int kTpMaxRanks = 8;
 constexpr int kTpMaxRows = 256;
+constexpr int kTpFlagInDataRanks = 4;  // widest group that exchanges with the flag inside every 8-byte word (see exchange_norm_kernel)
 constexpr size_t kTpFlagBytes = (size_t)2 * kTpMaxRanks * kTpMaxRows * sizeof(uint32_t);  // [2 slots][source rank][row]
 struct TpPeers {
   const void* xbuf[kTpMaxRanks];   // every rank's exchange buffer (own included), [2 slots][size sources][kTpMaxRows][hidden]
+                                   // (flag-in-data form: the same shape in 8-byte words of 2 elements + the exchange number)
   uint32_t* flags[kTpMaxRanks];    // every rank's flag array, [2][kTpMaxRanks][kTpMaxRows]
   uint32_t* seq;                   // local: two exchange counters 128 bytes apart, seq[0] for even launches, seq[32] for odd
   int rank, size;
+  int flag_in_data;                // 1: no flag array, every received word carries the exchange number
   int64_t slot_elems;              // kTpMaxRows * hidden
 };
 

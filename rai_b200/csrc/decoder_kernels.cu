@@ -123,6 +123,14 @@ __device__ __forceinline__ uint4 load16_sys(const void* p) {
   asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "l"(p) : "memory");
   return u;
 }
+// Two 8-byte words at system scope.  Each word is one scalar access of the memory model, so a reader sees a word
+// either whole or not at all: what the flag-in-data form of the exchange rests on.
+__device__ __forceinline__ void st_relaxed_sys_2x64(void* p, uint64_t a, uint64_t b) {
+  asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
+}
+__device__ __forceinline__ void ld_relaxed_sys_2x64(const void* p, uint64_t& a, uint64_t& b) {
+  asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
 __device__ __forceinline__ void add8_bf16(const uint4& u, float* v) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
 #pragma unroll
@@ -234,7 +242,13 @@ __global__ void __launch_bounds__(512) norm_vec_kernel(int kind, const T* __rest
 // Exchange numbers live on the device so that a captured graph replays unchanged: a launch with parity q reads
 // counter[q] (exchange number = counter[q] + 1) and, when done, sets counter[q ^ 1] to that number for the next
 // launch, whose parity is the opposite one; no launch writes the counter its own blocks read.
-template <typename T, int kChunks>
+//
+// kFlagInData (groups of up to kTpFlagInDataRanks): no flag array and no fence.  Every 8-byte word a peer receives
+// carries 4 bytes of payload and the exchange number; the receiver polls the words themselves until they all show
+// this exchange's number.  Twice the bytes on the wire, but the sender never waits for its stores to be acknowledged
+// and the receiver has the data the moment it has the flag: shorter by one NVLink round trip, which is what counts
+// while the message is small (wider groups move too many bytes for it and keep the flag array).
+template <typename T, int kChunks, bool kFlagInData>
 __global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* __restrict__ h, const float* __restrict__ acc, int n_acc,
                                      size_t acc_stride, const T* __restrict__ acc_bias, const T* __restrict__ part,
                                      const T* __restrict__ w, const T* __restrict__ b, float eps, int hidden,
@@ -280,12 +294,61 @@ __global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* _
       for (int i = 0; i < 8; ++i) v[i] += t[i]; }
     const uint4 packed = pack8_bf16(v);
     own[c] = packed;
+    if (kFlagInData) {
+      const uint64_t tag = (uint64_t)seq << 32;
+      const size_t word = (slot_off + (size_t)tp.rank * tp.slot_elems + base + ch * 8) >> 1;  // 2 elements per 8-byte word
 #pragma unroll
-    for (int r = 0; r < kTpMaxRanks; ++r)
-      if (r < tp.size && r != tp.rank)
-        *reinterpret_cast<uint4*>(reinterpret_cast<T*>(const_cast<void*>(tp.xbuf[r])) + slot_off + (size_t)tp.rank * tp.slot_elems +
-                                  base + ch * 8) = packed;
+      for (int r = 0; r < kTpFlagInDataRanks; ++r)
+        if (r < tp.size && r != tp.rank) {
+          uint64_t* dst = reinterpret_cast<uint64_t*>(const_cast<void*>(tp.xbuf[r])) + word;
+          st_relaxed_sys_2x64(dst, tag | packed.x, tag | packed.y);
+          st_relaxed_sys_2x64(dst + 2, tag | packed.z, tag | packed.w);
+        }
+    } else {
+#pragma unroll
+      for (int r = 0; r < kTpMaxRanks; ++r)
+        if (r < tp.size && r != tp.rank)
+          *reinterpret_cast<uint4*>(reinterpret_cast<T*>(const_cast<void*>(tp.xbuf[r])) + slot_off + (size_t)tp.rank * tp.slot_elems +
+                                    base + ch * 8) = packed;
+    }
   }
+  float v[kChunks][8];
+  if (kFlagInData) {
+    // ---- the same row from every peer: each thread polls the words it will sum (its own row is still in registers)
+    const long long t0 = clock64();
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+      const int ch = threadIdx.x + c * blockDim.x;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[c][i] = 0.f;
+      if (ch >= nchunk) continue;
+      uint4 pr[kTpFlagInDataRanks];
+      bool all = false;
+      while (!all) {
+        all = true;
+#pragma unroll
+        for (int r = 0; r < kTpFlagInDataRanks; ++r)
+          if (r < tp.size && r != tp.rank) {
+            const uint64_t* src = reinterpret_cast<const uint64_t*>(tp.xbuf[tp.rank]) +
+                                  ((slot_off + (size_t)r * tp.slot_elems + base + ch * 8) >> 1);
+            uint64_t a0, a1, a2, a3;
+            ld_relaxed_sys_2x64(src, a0, a1);
+            ld_relaxed_sys_2x64(src + 2, a2, a3);
+            all = all && (uint32_t)(a0 >> 32) == seq && (uint32_t)(a1 >> 32) == seq && (uint32_t)(a2 >> 32) == seq &&
+                  (uint32_t)(a3 >> 32) == seq;
+            pr[r] = make_uint4((uint32_t)a0, (uint32_t)a1, (uint32_t)a2, (uint32_t)a3);
+          }
+        if (!all && clock64() - t0 > wait_cycles) {
+          status[0] = (uint32_t)(-RB_ERR_TIMEOUT); status[1] = 0x7A11u; status[2] = (uint32_t)tp.rank; status[3] = seq;
+          give_up = 1u;
+          break;
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < kTpFlagInDataRanks; ++r)   // rank order, on every rank alike
+        if (r < tp.size) add8_bf16(r == tp.rank ? own[c] : pr[r], v[c]);
+    }
+  } else {
   __syncthreads();  // the block's stores are ordered before the releases below (cumulativity through the barrier)
   if ((int)threadIdx.x < tp.size) {
     // a release at system scope: every store of the block that the barrier ordered before it is performed at the peer
@@ -303,30 +366,41 @@ __global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* _
       }
     }
   }
+  }
   __syncthreads();
   // the exchange number moves on whether or not a peer arrived: the next launch must not reuse this one's slot
   if (row == 0 && threadIdx.x == 0) *reinterpret_cast<volatile uint32_t*>(tp.seq + (parity ^ 1) * 32) = seq;
   if (give_up) return;  // a peer never arrived: leave the outputs alone, the host sees the status
-  // the pollers' acquire loads plus the barrier order every thread's (system-scope) reads below behind the flags
-  float v[kChunks][8];
+  // (flag array form) the pollers' acquire loads plus the barrier order every thread's (system-scope) reads below
+  // behind the flags
   float s = 0.f;
   const float inv_sqrt_h = 1.0f / sqrtf((float)hidden);
   const T* mine = reinterpret_cast<const T*>(tp.xbuf[tp.rank]) + slot_off + base;
 #pragma unroll
   for (int c = 0; c < kChunks; ++c) {
     const int ch = threadIdx.x + c * blockDim.x;
+    if (ch >= nchunk) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[c][i] = 0.f;
-    if (ch >= nchunk) continue;
-    uint4 pr[kTpMaxRanks];  // all copies in flight at once, still packed
+      for (int i = 0; i < 8; ++i) v[c][i] = 0.f;
+      continue;
+    }
     float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (kFlagInData) {
 #pragma unroll
-    for (int r = 0; r < kTpMaxRanks; ++r)
-      if (r < tp.size) pr[r] = r == tp.rank ? own[c] : load16_sys(mine + (size_t)r * tp.slot_elems + ch * 8);
-    if (h) load8(h + base + ch * 8, v[c]);
+      for (int i = 0; i < 8; ++i) { sum[i] = v[c][i]; v[c][i] = 0.f; }
+      if (h) load8(h + base + ch * 8, v[c]);
+    } else {
+      uint4 pr[kTpMaxRanks];  // all copies in flight at once, still packed
 #pragma unroll
-    for (int r = 0; r < kTpMaxRanks; ++r)   // rank order, on every rank alike
-      if (r < tp.size) add8_bf16(pr[r], sum);
+      for (int i = 0; i < 8; ++i) v[c][i] = 0.f;
+#pragma unroll
+      for (int r = 0; r < kTpMaxRanks; ++r)
+        if (r < tp.size) pr[r] = r == tp.rank ? own[c] : load16_sys(mine + (size_t)r * tp.slot_elems + ch * 8);
+      if (h) load8(h + base + ch * 8, v[c]);
+#pragma unroll
+      for (int r = 0; r < kTpMaxRanks; ++r)   // rank order, on every rank alike
+        if (r < tp.size) add8_bf16(pr[r], sum);
+    }
     round_to<T>(sum);  // what an allreduce in the model dtype would have delivered
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[c][i] += sum[i];
@@ -789,9 +863,16 @@ int exchange_norm(rb_ctx* ctx, const TpPeers& tp, int parity, int kind, const vo
                          acc_stride, (const T*)acc_bias, (const T*)part, (const T*)w, (const T*)b, eps, (int)hidden, (T*)out,
                          (T*)sum_out, tp, parity, ctx->status_dev, ctx->wait_budget_cycles);
   };
-  if (chunks == 1) RB_CUDA(go(exchange_norm_kernel<T, 1>));
-  else if (chunks == 2) RB_CUDA(go(exchange_norm_kernel<T, 2>));
-  else RB_CUDA(go(exchange_norm_kernel<T, 4>));
+  if (tp.flag_in_data) {
+    RB_REQUIRE(tp.size <= kTpFlagInDataRanks, "exchange_norm: the flag-in-data form takes groups of up to %d", kTpFlagInDataRanks);
+    if (chunks == 1) RB_CUDA(go(exchange_norm_kernel<T, 1, true>));
+    else if (chunks == 2) RB_CUDA(go(exchange_norm_kernel<T, 2, true>));
+    else RB_CUDA(go(exchange_norm_kernel<T, 4, true>));
+  } else {
+    if (chunks == 1) RB_CUDA(go(exchange_norm_kernel<T, 1, false>));
+    else if (chunks == 2) RB_CUDA(go(exchange_norm_kernel<T, 2, false>));
+    else RB_CUDA(go(exchange_norm_kernel<T, 4, false>));
+  }
   ctx->launches++;
   return RB_OK;
 }

@@ -499,7 +499,12 @@ extern "C" int32_t rb_model_tp_init(rb_model* m, const void* id, int32_t id_byte
   rb_ctx* ctx = m->ctx;
   const int tp = m->cfg.tp_size, rank = m->cfg.tp_rank;
   const size_t slot_elems = (size_t)kTpMaxRows * m->cfg.hidden_size;
-  const size_t bytes = kTpFlagBytes + 2 * (size_t)tp * slot_elems * 2;  // flags, then [2 slots][tp sources][rows x hidden] bf16
+  // Groups of up to four exchange with the flag inside every 8-byte word (one NVLink round trip shorter, twice the
+  // bytes); wider groups keep the flag array.  RAI_B200_TP_FLAG_IN_DATA=0/1 overrides (the same on every rank).
+  bool flag_in_data = tp <= kTpFlagInDataRanks;
+  if (const char* fd = getenv("RAI_B200_TP_FLAG_IN_DATA")) flag_in_data = fd[0] == '1' && tp <= kTpFlagInDataRanks;
+  // flags, then [2 slots][tp sources][rows x hidden] bf16 (4 bytes per element instead of 2 with the flag in the data)
+  const size_t bytes = kTpFlagBytes + 2 * (size_t)tp * slot_elems * (flag_in_data ? 4 : 2);
   RB_TRY(rb_malloc(ctx, bytes, &m->xchg_base));
   m->owned.push_back(m->xchg_base);
   RB_CUDA(cudaMemsetAsync(m->xchg_base, 0, bytes, ctx->stream));
@@ -554,6 +559,7 @@ extern "C" int32_t rb_model_tp_init(rb_model* m, const void* id, int32_t id_byte
   RB_CUDA(cudaMemsetAsync(local, 0, 256, ctx->stream));
   p.seq = (uint32_t*)local;
   p.rank = rank; p.size = tp; p.slot_elems = (int64_t)slot_elems;
+  p.flag_in_data = flag_in_data ? 1 : 0;
   // (the vote above was also the meeting point: no rank publishes before every rank has zeroed its region and
   // opened its peers)
   RB_CUDA(cudaStreamSynchronize(ctx->stream));
@@ -769,7 +775,7 @@ extern "C" int32_t rb_model_create(rb_ctx* ctx, const rb_model_config* cfg, rb_m
       p.flags[0] = (uint32_t*)m->xchg_base;
       p.seq = (uint32_t*)((char*)m->xchg_base + kTpFlagBytes);
       p.xbuf[0] = (const char*)m->xchg_base + kTpFlagBytes + 512;
-      p.rank = 0; p.size = 1; p.slot_elems = (int64_t)slot_elems;
+      p.rank = 0; p.size = 1; p.slot_elems = (int64_t)slot_elems; p.flag_in_data = 0;
       m->peer_base[0] = m->xchg_base;
       m->use_exchange = true;
     }
