@@ -246,8 +246,9 @@ __global__ void __launch_bounds__(512) norm_vec_kernel(int kind, const T* __rest
 // kFlagInData (groups of up to kTpFlagInDataRanks): no flag array and no fence.  Every 8-byte word a peer receives
 // carries 4 bytes of payload and the exchange number; the receiver polls the words themselves until they all show
 // this exchange's number.  Twice the bytes on the wire, but the sender never waits for its stores to be acknowledged
-// and the receiver has the data the moment it has the flag: shorter by one NVLink round trip, which is what counts
-// while the message is small (wider groups move too many bytes for it and keep the flag array).
+// and the receiver has the data the moment it has the flag: shorter by one NVLink round trip.  That pays between two
+// GPUs (3.43 -> 3.19-3.29 ms per decode step of the 7B model); among four the doubled bytes already cost more than
+// the round trip saves (2.79-2.82 against 2.73 ms), so wider groups keep the flag array.
 template <typename T, int kChunks, bool kFlagInData>
 __global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* __restrict__ h, const float* __restrict__ acc, int n_acc,
                                      size_t acc_stride, const T* __restrict__ acc_bias, const T* __restrict__ part,

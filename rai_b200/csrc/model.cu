@@ -499,8 +499,8 @@ extern "C" int32_t rb_model_tp_init(rb_model* m, const void* id, int32_t id_byte
   rb_ctx* ctx = m->ctx;
   const int tp = m->cfg.tp_size, rank = m->cfg.tp_rank;
   const size_t slot_elems = (size_t)kTpMaxRows * m->cfg.hidden_size;
-  // Groups of up to four exchange with the flag inside every 8-byte word (one NVLink round trip shorter, twice the
-  // bytes); wider groups keep the flag array.  RAI_B200_TP_FLAG_IN_DATA=0/1 overrides (the same on every rank).
+  // A group of two exchanges with the flag inside every 8-byte word (one NVLink round trip shorter, twice the
+  // bytes); wider groups keep the flag array.  RAI_B200_TP_FLAG_IN_DATA=0 turns it off (the same on every rank).
   bool flag_in_data = tp <= kTpFlagInDataRanks;
   if (const char* fd = getenv("RAI_B200_TP_FLAG_IN_DATA")) flag_in_data = fd[0] == '1' && tp <= kTpFlagInDataRanks;
   // flags, then [2 slots][tp sources][rows x hidden] bf16 (4 bytes per element instead of 2 with the flag in the data)
