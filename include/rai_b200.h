@@ -98,7 +98,8 @@ int32_t rb_set_wait_budget_us(rb_ctx* ctx, int64_t microseconds);
 /* Self-test of the give-up path, for test suites: runs a kernel whose wait can never be satisfied (`which` 0: an
  * mbarrier nothing arrives on, waited for with the library's own helper; 1: the tensor-parallel exchange of a
  * two-member group whose second member, zeroed memory of this GPU, never raises its flag; 2: the same exchange
- * in its flag-inside-the-data form, whose second member's words never show the exchange number), with the given
+ * in its flag-inside-the-data form, whose second member's words never show the exchange number; 3: that form over
+ * two hops, where one row waits for the other member's share and the other row for its finished sum), with the given
  * budget.  The kernel returns when the budget runs out; RB_OK means the give-up was recorded as designed
  * (RB_ERR_TIMEOUT with the kernel's tag, outputs untouched), and the status word is clear again on return.
  * Nothing faults, traps or spins without bound.  No counterpart in the reference. */

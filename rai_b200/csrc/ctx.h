@@ -79,7 +79,8 @@ constexpr int kGemmMaxReduceTiles = 256;
 
 constexpr int kTpMaxRanks = 8;
 constexpr int kTpMaxRows = 256;
-constexpr int kTpFlagInDataRanks = 2;  // widest group that exchanges with the flag inside every 8-byte word (see exchange_norm_kernel)
+constexpr int kTpFlagInDataRanks = 2;  // widest group that exchanges with the flag inside every 8-byte word, directly (see exchange_norm_kernel)
+constexpr int kTpTwoHopRanks = 4;      // widest group that takes the two-hop form of it by default
 constexpr size_t kTpFlagBytes = (size_t)2 * kTpMaxRanks * kTpMaxRows * sizeof(uint32_t);  // [2 slots][source rank][row]
 struct TpPeers {
   const void* xbuf[kTpMaxRanks];   // every rank's exchange buffer (own included), [2 slots][size sources][kTpMaxRows][hidden]
@@ -87,7 +88,7 @@ struct TpPeers {
   uint32_t* flags[kTpMaxRanks];    // every rank's flag array, [2][kTpMaxRanks][kTpMaxRows]
   uint32_t* seq;                   // local: two exchange counters 128 bytes apart, seq[0] for even launches, seq[32] for odd
   int rank, size;
-  int flag_in_data;                // 1: no flag array, every received word carries the exchange number
+  int flag_in_data;                // 0: flag array; 1: every received word carries the exchange number; 2: the same, two hops through a row's owner
   int64_t slot_elems;              // kTpMaxRows * hidden
 };
 

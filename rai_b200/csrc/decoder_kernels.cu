@@ -243,13 +243,19 @@ __global__ void __launch_bounds__(512) norm_vec_kernel(int kind, const T* __rest
 // counter[q] (exchange number = counter[q] + 1) and, when done, sets counter[q ^ 1] to that number for the next
 // launch, whose parity is the opposite one; no launch writes the counter its own blocks read.
 //
-// kFlagInData (groups of up to kTpFlagInDataRanks): no flag array and no fence.  Every 8-byte word a peer receives
+// kMode 1, flag in the data, direct (a group of two): no flag array and no fence.  Every 8-byte word a peer receives
 // carries 4 bytes of payload and the exchange number; the receiver polls the words themselves until they all show
 // this exchange's number.  Twice the bytes on the wire, but the sender never waits for its stores to be acknowledged
 // and the receiver has the data the moment it has the flag: shorter by one NVLink round trip.  That pays between two
 // GPUs (3.43 -> 3.19-3.29 ms per decode step of the 7B model); among four the doubled bytes already cost more than
-// the round trip saves (2.79-2.82 against 2.73 ms), so wider groups keep the flag array.
-template <typename T, int kChunks, bool kFlagInData>
+// the round trip saves (2.79-2.82 against 2.73 ms).
+//
+// kMode 2, flag in the data, two hops (wider groups): row r has an owner, rank r % size.  The other ranks send their
+// partial row to the owner only; the owner sums the copies in rank order, rounds, and sends the finished row to
+// everyone.  Two one-way trips instead of a push, a fence and a flag, and 2 (size - 1) / size rows per rank and
+// exchange on the wire instead of size - 1 (or twice that with the flag in the data).  Every rank gets the same
+// bits, since only the owner adds.
+template <typename T, int kChunks, int kMode>
 __global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* __restrict__ h, const float* __restrict__ acc, int n_acc,
                                      size_t acc_stride, const T* __restrict__ acc_bias, const T* __restrict__ part,
                                      const T* __restrict__ w, const T* __restrict__ b, float eps, int hidden,
@@ -295,7 +301,7 @@ __global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* _
       for (int i = 0; i < 8; ++i) v[i] += t[i]; }
     const uint4 packed = pack8_bf16(v);
     own[c] = packed;
-    if (kFlagInData) {
+    if (kMode == 1) {
       const uint64_t tag = (uint64_t)seq << 32;
       const size_t word = (slot_off + (size_t)tp.rank * tp.slot_elems + base + ch * 8) >> 1;  // 2 elements per 8-byte word
 #pragma unroll
@@ -305,6 +311,15 @@ __global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* _
           st_relaxed_sys_2x64(dst, tag | packed.x, tag | packed.y);
           st_relaxed_sys_2x64(dst + 2, tag | packed.z, tag | packed.w);
         }
+    } else if (kMode == 2) {
+      const int owner = row % tp.size;
+      if (owner != tp.rank) {   // this rank's share of the row goes to the row's owner only
+        const uint64_t tag = (uint64_t)seq << 32;
+        uint64_t* dst = reinterpret_cast<uint64_t*>(const_cast<void*>(tp.xbuf[owner])) +
+                        ((slot_off + (size_t)tp.rank * tp.slot_elems + base + ch * 8) >> 1);
+        st_relaxed_sys_2x64(dst, tag | packed.x, tag | packed.y);
+        st_relaxed_sys_2x64(dst + 2, tag | packed.z, tag | packed.w);
+      }
     } else {
 #pragma unroll
       for (int r = 0; r < kTpMaxRanks; ++r)
@@ -314,7 +329,78 @@ __global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* _
     }
   }
   float v[kChunks][8];
-  if (kFlagInData) {
+  if (kMode == 2) {
+    const int owner = row % tp.size;
+    const uint64_t tag = (uint64_t)seq << 32;
+    // finished rows live behind the 2 x size gathering slots: [2 slots][rows x hidden]
+    const size_t res_off = (size_t)2 * tp.size * tp.slot_elems + (size_t)(seq & 1u) * tp.slot_elems;
+    const long long t0 = clock64();
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+      const int ch = threadIdx.x + c * blockDim.x;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[c][i] = 0.f;
+      if (ch >= nchunk) continue;
+      if (owner == tp.rank) {
+        // ---- the owner: every other rank's share of this row, summed in rank order with its own, sent to everyone
+        uint4 pr[kTpMaxRanks];
+        bool all = false;
+        while (!all) {
+          all = true;
+#pragma unroll
+          for (int r = 0; r < kTpMaxRanks; ++r)
+            if (r < tp.size && r != tp.rank) {
+              const uint64_t* src = reinterpret_cast<const uint64_t*>(tp.xbuf[tp.rank]) +
+                                    ((slot_off + (size_t)r * tp.slot_elems + base + ch * 8) >> 1);
+              uint64_t a0, a1, a2, a3;
+              ld_relaxed_sys_2x64(src, a0, a1);
+              ld_relaxed_sys_2x64(src + 2, a2, a3);
+              all = all && (uint32_t)(a0 >> 32) == seq && (uint32_t)(a1 >> 32) == seq && (uint32_t)(a2 >> 32) == seq &&
+                    (uint32_t)(a3 >> 32) == seq;
+              pr[r] = make_uint4((uint32_t)a0, (uint32_t)a1, (uint32_t)a2, (uint32_t)a3);
+            }
+          if (!all && clock64() - t0 > wait_cycles) {
+            status[0] = (uint32_t)(-RB_ERR_TIMEOUT); status[1] = 0x7A11u; status[2] = (uint32_t)tp.rank; status[3] = seq;
+            give_up = 1u;
+            break;
+          }
+        }
+        if (!all) continue;
+        float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < kTpMaxRanks; ++r)   // rank order
+          if (r < tp.size) add8_bf16(r == tp.rank ? own[c] : pr[r], sum);
+        const uint4 red = pack8_bf16(sum);  // what an allreduce in the model dtype would have delivered
+        const size_t word = (res_off + base + ch * 8) >> 1;
+#pragma unroll
+        for (int r = 0; r < kTpMaxRanks; ++r)
+          if (r < tp.size && r != tp.rank) {
+            uint64_t* dst = reinterpret_cast<uint64_t*>(const_cast<void*>(tp.xbuf[r])) + word;
+            st_relaxed_sys_2x64(dst, tag | red.x, tag | red.y);
+            st_relaxed_sys_2x64(dst + 2, tag | red.z, tag | red.w);
+          }
+        add8_bf16(red, v[c]);
+      } else {
+        // ---- everyone else: the finished row from its owner
+        const uint64_t* src = reinterpret_cast<const uint64_t*>(tp.xbuf[tp.rank]) + ((res_off + base + ch * 8) >> 1);
+        uint64_t a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+        bool all = false;
+        while (!all) {
+          ld_relaxed_sys_2x64(src, a0, a1);
+          ld_relaxed_sys_2x64(src + 2, a2, a3);
+          all = (uint32_t)(a0 >> 32) == seq && (uint32_t)(a1 >> 32) == seq && (uint32_t)(a2 >> 32) == seq &&
+                (uint32_t)(a3 >> 32) == seq;
+          if (!all && clock64() - t0 > wait_cycles) {
+            status[0] = (uint32_t)(-RB_ERR_TIMEOUT); status[1] = 0x7A11u; status[2] = (uint32_t)tp.rank; status[3] = seq;
+            give_up = 1u;
+            break;
+          }
+        }
+        if (!all) continue;
+        add8_bf16(make_uint4((uint32_t)a0, (uint32_t)a1, (uint32_t)a2, (uint32_t)a3), v[c]);
+      }
+    }
+  } else if (kMode == 1) {
     // ---- the same row from every peer: each thread polls the words it will sum (its own row is still in registers)
     const long long t0 = clock64();
 #pragma unroll
@@ -386,7 +472,7 @@ __global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* _
       continue;
     }
     float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (kFlagInData) {
+    if (kMode != 0) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) { sum[i] = v[c][i]; v[c][i] = 0.f; }
       if (h) load8(h + base + ch * 8, v[c]);
@@ -864,15 +950,19 @@ int exchange_norm(rb_ctx* ctx, const TpPeers& tp, int parity, int kind, const vo
                          acc_stride, (const T*)acc_bias, (const T*)part, (const T*)w, (const T*)b, eps, (int)hidden, (T*)out,
                          (T*)sum_out, tp, parity, ctx->status_dev, ctx->wait_budget_cycles);
   };
-  if (tp.flag_in_data) {
-    RB_REQUIRE(tp.size <= kTpFlagInDataRanks, "exchange_norm: the flag-in-data form takes groups of up to %d", kTpFlagInDataRanks);
-    if (chunks == 1) RB_CUDA(go(exchange_norm_kernel<T, 1, true>));
-    else if (chunks == 2) RB_CUDA(go(exchange_norm_kernel<T, 2, true>));
-    else RB_CUDA(go(exchange_norm_kernel<T, 4, true>));
+  if (tp.flag_in_data == 1) {
+    RB_REQUIRE(tp.size <= kTpFlagInDataRanks, "exchange_norm: the direct flag-in-data form takes groups of up to %d", kTpFlagInDataRanks);
+    if (chunks == 1) RB_CUDA(go(exchange_norm_kernel<T, 1, 1>));
+    else if (chunks == 2) RB_CUDA(go(exchange_norm_kernel<T, 2, 1>));
+    else RB_CUDA(go(exchange_norm_kernel<T, 4, 1>));
+  } else if (tp.flag_in_data == 2) {
+    if (chunks == 1) RB_CUDA(go(exchange_norm_kernel<T, 1, 2>));
+    else if (chunks == 2) RB_CUDA(go(exchange_norm_kernel<T, 2, 2>));
+    else RB_CUDA(go(exchange_norm_kernel<T, 4, 2>));
   } else {
-    if (chunks == 1) RB_CUDA(go(exchange_norm_kernel<T, 1, false>));
-    else if (chunks == 2) RB_CUDA(go(exchange_norm_kernel<T, 2, false>));
-    else RB_CUDA(go(exchange_norm_kernel<T, 4, false>));
+    if (chunks == 1) RB_CUDA(go(exchange_norm_kernel<T, 1, 0>));
+    else if (chunks == 2) RB_CUDA(go(exchange_norm_kernel<T, 2, 0>));
+    else RB_CUDA(go(exchange_norm_kernel<T, 4, 0>));
   }
   ctx->launches++;
   return RB_OK;

@@ -499,12 +499,18 @@ extern "C" int32_t rb_model_tp_init(rb_model* m, const void* id, int32_t id_byte
   rb_ctx* ctx = m->ctx;
   const int tp = m->cfg.tp_size, rank = m->cfg.tp_rank;
   const size_t slot_elems = (size_t)kTpMaxRows * m->cfg.hidden_size;
-  // A group of two exchanges with the flag inside every 8-byte word (one NVLink round trip shorter, twice the
-  // bytes); wider groups keep the flag array.  RAI_B200_TP_FLAG_IN_DATA=0 turns it off (the same on every rank).
-  bool flag_in_data = tp <= kTpFlagInDataRanks;
-  if (const char* fd = getenv("RAI_B200_TP_FLAG_IN_DATA")) flag_in_data = fd[0] == '1' && tp <= kTpFlagInDataRanks;
-  // flags, then [2 slots][tp sources][rows x hidden] bf16 (4 bytes per element instead of 2 with the flag in the data)
-  const size_t bytes = kTpFlagBytes + 2 * (size_t)tp * slot_elems * (flag_in_data ? 4 : 2);
+  // How the exchange signals arrival (see exchange_norm_kernel): 0 = a flag array beside the data; 1 = the flag inside
+  // every 8-byte word, sent straight to every peer (a group of two); 2 = the same words over two hops through the
+  // row's owner (a group of four).  RAI_B200_TP_FLAG_IN_DATA=0/1/2 overrides (the same on every rank).
+  int mode = tp <= kTpFlagInDataRanks ? 1 : tp <= kTpTwoHopRanks ? 2 : 0;
+  if (const char* fd = getenv("RAI_B200_TP_FLAG_IN_DATA")) {
+    const int want = atoi(fd);
+    if (want == 0 || want == 2 || (want == 1 && tp <= kTpFlagInDataRanks)) mode = want;
+  }
+  // flags, then [2 slots][tp sources][rows x hidden] bf16 (4 bytes per element instead of 2 with the flag in the data;
+  // the two-hop form adds [2 slots][rows x hidden] for the finished rows)
+  const size_t bytes = kTpFlagBytes + (mode == 0 ? 2 * (size_t)tp * slot_elems * 2
+                                                  : (2 * (size_t)tp + (mode == 2 ? 2 : 0)) * slot_elems * 4);
   RB_TRY(rb_malloc(ctx, bytes, &m->xchg_base));
   m->owned.push_back(m->xchg_base);
   RB_CUDA(cudaMemsetAsync(m->xchg_base, 0, bytes, ctx->stream));
@@ -559,7 +565,7 @@ extern "C" int32_t rb_model_tp_init(rb_model* m, const void* id, int32_t id_byte
   RB_CUDA(cudaMemsetAsync(local, 0, 256, ctx->stream));
   p.seq = (uint32_t*)local;
   p.rank = rank; p.size = tp; p.slot_elems = (int64_t)slot_elems;
-  p.flag_in_data = flag_in_data ? 1 : 0;
+  p.flag_in_data = mode;
   // (the vote above was also the meeting point: no rank publishes before every rank has zeroed its region and
   // opened its peers)
   RB_CUDA(cudaStreamSynchronize(ctx->stream));

@@ -45,7 +45,7 @@ using namespace rb;
 
 extern "C" int32_t rb_selftest_wait_gives_up(rb_ctx* ctx, int32_t which, int64_t budget_us) {
   RB_REQUIRE(ctx, "rb_selftest_wait_gives_up: null context");
-  RB_REQUIRE(which >= 0 && which <= 2, "rb_selftest_wait_gives_up: unknown test %d", which);
+  RB_REQUIRE(which >= 0 && which <= 3, "rb_selftest_wait_gives_up: unknown test %d", which);
   RB_REQUIRE(budget_us >= 1 && budget_us <= 1000000, "rb_selftest_wait_gives_up: budget %lld us outside [1, 1 000 000]",
              (long long)budget_us);
   RB_TRY(rb_sync(ctx));  // start from a clear status word
@@ -67,12 +67,14 @@ extern "C" int32_t rb_selftest_wait_gives_up(rb_ctx* ctx, int32_t which, int64_t
     return RB_OK;
   }
   // ---- the tensor-parallel exchange over a two-member group that lives entirely in this GPU's memory; this launch
-  // plays member 0 and nobody plays member 1.  which == 1: the flag-array form; which == 2: the flag inside the data.
-  const bool in_data = which == 2;
+  // plays member 0 and nobody plays member 1.  which == 1: the flag-array form; 2: the flag inside the data, direct;
+  // 3: the flag inside the data over two hops (row 0 is member 0's to finish, row 1 member 1's).
+  const bool in_data = which >= 2;
+  const bool two_hop = which == 3;
   const int rows = 2, hidden = 256;
   DevBuf region, part, h, wt, out, sum;
   const size_t slot_elems = (size_t)kTpMaxRows * hidden;
-  const size_t region_bytes = kTpFlagBytes + 512 + 2 * 2 * slot_elems * (in_data ? 4 : 2);   // flags | counters | 2 slots x 2 sources
+  const size_t region_bytes = kTpFlagBytes + 512 + (2 * 2 + (two_hop ? 2 : 0)) * slot_elems * (in_data ? 4 : 2);   // flags | counters | 2 slots x 2 sources (| 2 slots of finished rows)
   const size_t act_bytes = (size_t)rows * hidden * 2;
   RB_CUDA(cudaMalloc(&region.p, region_bytes));
   RB_CUDA(cudaMalloc(&part.p, act_bytes));
@@ -92,7 +94,7 @@ extern "C" int32_t rb_selftest_wait_gives_up(rb_ctx* ctx, int32_t which, int64_t
   tp.flags[0] = tp.flags[1] = flags;
   tp.seq = (uint32_t*)((char*)region.p + kTpFlagBytes);
   tp.xbuf[0] = tp.xbuf[1] = (const char*)region.p + kTpFlagBytes + 512;
-  tp.rank = 0; tp.size = 2; tp.slot_elems = (int64_t)slot_elems; tp.flag_in_data = in_data ? 1 : 0;
+  tp.rank = 0; tp.size = 2; tp.slot_elems = (int64_t)slot_elems; tp.flag_in_data = two_hop ? 2 : in_data ? 1 : 0;
   RB_CUDA(cudaStreamSynchronize(ctx->stream));  // the host buffers above are read by the copies
   const long long keep = ctx->wait_budget_cycles;
   ctx->wait_budget_cycles = budget;
@@ -112,7 +114,18 @@ extern "C" int32_t rb_selftest_wait_gives_up(rb_ctx* ctx, int32_t which, int64_t
                 "outputs %s", w[0], w[1], untouched ? "untouched" : "written");
   // exchange number 2 (parity 1, slot 0) with member 1's rows "arrived" (all zero) and its flags raised: completes,
   // nothing recorded, and the sum is member 0's term alone
-  if (in_data) {
+  if (two_hop) {
+    // exchange 2 lands in slot 0.  Row 0 is ours to finish: member 1's share of it (payload 0) arrives in the
+    // gathering slot; row 1 is member 1's: its finished row (1 + 0 = bf16 1.0 in every element) arrives behind the
+    // gathering slots
+    uint64_t* words0 = (uint64_t*)((char*)region.p + kTpFlagBytes + 512);
+    std::vector<uint64_t> share((size_t)hidden / 2, (uint64_t)2u << 32);
+    std::vector<uint64_t> done((size_t)hidden / 2, ((uint64_t)2u << 32) | 0x3F803F80u);
+    RB_CUDA(cudaMemcpy(words0 + ((((size_t)0 * 2 + 1) * slot_elems + (size_t)0 * hidden) >> 1), share.data(),
+                       share.size() * sizeof(uint64_t), cudaMemcpyHostToDevice));
+    RB_CUDA(cudaMemcpy(words0 + (((size_t)2 * 2 * slot_elems + (size_t)0 * slot_elems + (size_t)1 * hidden) >> 1), done.data(),
+                       done.size() * sizeof(uint64_t), cudaMemcpyHostToDevice));
+  } else if (in_data) {
     // member 1's two rows of slot 0: every 8-byte word = payload 0, exchange number 2
     std::vector<uint64_t> words((size_t)rows * hidden / 2, (uint64_t)2u << 32);
     uint64_t* dst = (uint64_t*)((char*)region.p + kTpFlagBytes + 512) + (((size_t)0 * 2 + 1) * slot_elems >> 1);

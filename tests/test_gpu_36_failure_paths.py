@@ -31,7 +31,8 @@ def small_linear_is_right(cuda, seed):
 
 @pytest.mark.parametrize("which,what", [(0, "an mbarrier nobody arrives on"),
                                         (1, "a tensor-parallel peer that never raises its flag"),
-                                        (2, "a tensor-parallel peer whose words never show the exchange number")])
+                                        (2, "a tensor-parallel peer whose words never show the exchange number"),
+                                        (3, "a row's owner that never sends the finished row")])
 def test_a_wait_that_cannot_be_satisfied_gives_up_and_reports(cuda, which, what):
     t0 = time.time()
     _lib.call("rb_selftest_wait_gives_up", cuda.ctx, which, 2000)     # 2 ms budget; raises if anything is off
