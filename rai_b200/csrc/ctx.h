@@ -80,7 +80,7 @@ constexpr int kGemmMaxReduceTiles = 256;
 constexpr int kTpMaxRanks = 8;
 constexpr int kTpMaxRows = 256;
 constexpr int kTpFlagInDataRanks = 2;  // widest group that exchanges with the flag inside every 8-byte word, directly (see exchange_norm_kernel)
-constexpr int kTpTwoHopRanks = 4;      // widest group that takes the two-hop form of it by default
+constexpr int kTpTwoHopRanks = 8;      // widest group that takes the two-hop form of it by default
 constexpr size_t kTpFlagBytes = (size_t)2 * kTpMaxRanks * kTpMaxRows * sizeof(uint32_t);  // [2 slots][source rank][row]
 struct TpPeers {
   const void* xbuf[kTpMaxRanks];   // every rank's exchange buffer (own included), [2 slots][size sources][kTpMaxRows][hidden]

@@ -501,7 +501,7 @@ extern "C" int32_t rb_model_tp_init(rb_model* m, const void* id, int32_t id_byte
   const size_t slot_elems = (size_t)kTpMaxRows * m->cfg.hidden_size;
   // How the exchange signals arrival (see exchange_norm_kernel): 0 = a flag array beside the data; 1 = the flag inside
   // every 8-byte word, sent straight to every peer (a group of two); 2 = the same words over two hops through the
-  // row's owner (a group of four).  RAI_B200_TP_FLAG_IN_DATA=0/1/2 overrides (the same on every rank).
+  // row's owner (wider groups).  RAI_B200_TP_FLAG_IN_DATA=0/1/2 overrides (the same on every rank).
   int mode = tp <= kTpFlagInDataRanks ? 1 : tp <= kTpTwoHopRanks ? 2 : 0;
   if (const char* fd = getenv("RAI_B200_TP_FLAG_IN_DATA")) {
     const int want = atoi(fd);
