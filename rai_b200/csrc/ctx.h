@@ -66,21 +66,25 @@ struct rb_kv_cache {
   size_t layer_stride_elems() const { return (size_t)num_pages * kv_heads * 64 * head_dim; }
 };
 
-// Peer-memory exchange of a tensor-parallel group for decode-sized allreduces: every rank pushes its partial
-// [rows, hidden] into its own place in EVERY rank's exchange buffer (posted stores over NVLink, no round trip); the
-// block that pushed row r then raises, after one system-scope fence, the flag of (source rank, row r) in every peer's
-// flag array, waits (bounded) for that row's flag from every rank - it does not wait for the other rows - and sums
-// the copies in its own memory in rank order, the same on every rank.  Two slots, chosen by the parity of an exchange
-// number kept on the device, so replayed CUDA graphs need no new arguments: launches alternate between two local
-// counters (a launch reads one and sets the other for its successor), so no kernel changes a word its own blocks are
-// still reading.  Slot n & 1 is free again when exchange n + 2 starts: a rank gets there only after every rank has
-// raised its flags of exchange n + 1, which a rank does only after its own exchange n has completed.
+// Peer-memory exchange of a tensor-parallel group for decode-sized allreduces (exchange_norm_kernel, one block per
+// row).  Flag-array form: every rank stores its partial row into its own place in every PEER's exchange buffer (posted
+// stores over NVLink), raises the flag of (source rank, row) in every peer's flag array with a system-scope release,
+// waits (bounded) for that row's flag from every peer - not for the other rows - and sums the copies in its own memory
+// and its own row in rank order, the same on every rank.  The two flag-in-data forms need no flag array: every
+// 8-byte word carries 4 bytes of payload and the exchange number (see the kernel).  Two slots, chosen by the parity
+// of an exchange number kept on the device, so replayed CUDA graphs need no new arguments: launches alternate
+// between two local counters (a launch reads one and sets the other for its successor), so no kernel changes a word
+// its own blocks are still reading.  Slot n & 1 is free again when exchange n + 2 starts: a rank gets there only
+// after every rank has delivered its rows of exchange n + 1, which a rank does only after its own exchange n has
+// completed.
 constexpr int kGemmMaxReduceTiles = 256;
 
 constexpr int kTpMaxRanks = 8;
 constexpr int kTpMaxRows = 256;
-constexpr int kTpFlagInDataRanks = 2;  // widest group that exchanges with the flag inside every 8-byte word, directly (see exchange_norm_kernel)
-constexpr int kTpTwoHopRanks = 8;      // widest group that takes the two-hop form of it by default
+// Forms of the exchange (see exchange_norm_kernel): how arrival is signalled and which way the rows travel.
+enum TpForm : int { kTpFlagArray = 0, kTpInDataDirect = 1, kTpInDataTwoHop = 2 };
+constexpr int kTpDirectRanks = 2;      // widest group that sends flag-in-data words straight to every peer
+constexpr int kTpTwoHopRanks = 8;      // widest group that takes the two-hop form of them by default
 constexpr size_t kTpFlagBytes = (size_t)2 * kTpMaxRanks * kTpMaxRows * sizeof(uint32_t);  // [2 slots][source rank][row]
 struct TpPeers {
   const void* xbuf[kTpMaxRanks];   // every rank's exchange buffer (own included), [2 slots][size sources][kTpMaxRows][hidden]
@@ -88,7 +92,7 @@ struct TpPeers {
   uint32_t* flags[kTpMaxRanks];    // every rank's flag array, [2][kTpMaxRanks][kTpMaxRows]
   uint32_t* seq;                   // local: two exchange counters 128 bytes apart, seq[0] for even launches, seq[32] for odd
   int rank, size;
-  int flag_in_data;                // 0: flag array; 1: every received word carries the exchange number; 2: the same, two hops through a row's owner
+  int form;                        // a TpForm
   int64_t slot_elems;              // kTpMaxRows * hidden
 };
 

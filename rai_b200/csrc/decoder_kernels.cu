@@ -243,14 +243,14 @@ __global__ void __launch_bounds__(512) norm_vec_kernel(int kind, const T* __rest
 // counter[q] (exchange number = counter[q] + 1) and, when done, sets counter[q ^ 1] to that number for the next
 // launch, whose parity is the opposite one; no launch writes the counter its own blocks read.
 //
-// kMode 1, flag in the data, direct (a group of two): no flag array and no fence.  Every 8-byte word a peer receives
+// kTpInDataDirect, flag in the data, direct (a group of two): no flag array and no fence.  Every 8-byte word a peer receives
 // carries 4 bytes of payload and the exchange number; the receiver polls the words themselves until they all show
 // this exchange's number.  Twice the bytes on the wire, but the sender never waits for its stores to be acknowledged
 // and the receiver has the data the moment it has the flag: shorter by one NVLink round trip.  That pays between two
 // GPUs (3.43 -> 3.19-3.29 ms per decode step of the 7B model); among four the doubled bytes already cost more than
 // the round trip saves (2.79-2.82 against 2.73 ms).
 //
-// kMode 2, flag in the data, two hops (wider groups): row r has an owner, rank r % size.  The other ranks send their
+// kTpInDataTwoHop, flag in the data, two hops (wider groups): row r has an owner, rank r % size.  The other ranks send their
 // partial row to the owner only; the owner sums the copies in rank order, rounds, and sends the finished row to
 // everyone.  Two one-way trips instead of a push, a fence and a flag, and 2 (size - 1) / size rows per rank and
 // exchange on the wire instead of size - 1 (or twice that with the flag in the data).  Every rank gets the same
@@ -302,17 +302,17 @@ __global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* _
       for (int i = 0; i < 8; ++i) v[i] += t[i]; }
     const uint4 packed = pack8_bf16(v);
     own[c] = packed;
-    if (kMode == 1) {
+    if (kMode == kTpInDataDirect) {
       const uint64_t tag = (uint64_t)seq << 32;
       const size_t word = (slot_off + (size_t)tp.rank * tp.slot_elems + base + ch * 8) >> 1;  // 2 elements per 8-byte word
 #pragma unroll
-      for (int r = 0; r < kTpFlagInDataRanks; ++r)
+      for (int r = 0; r < kTpDirectRanks; ++r)
         if (r < tp.size && r != tp.rank) {
           uint64_t* dst = reinterpret_cast<uint64_t*>(const_cast<void*>(tp.xbuf[r])) + word;
           st_relaxed_sys_2x64(dst, tag | packed.x, tag | packed.y);
           st_relaxed_sys_2x64(dst + 2, tag | packed.z, tag | packed.w);
         }
-    } else if (kMode == 2) {
+    } else if (kMode == kTpInDataTwoHop) {
       const int owner = row % tp.size;
       if (owner != tp.rank) {   // this rank's share of the row goes to the row's owner only
         const uint64_t tag = (uint64_t)seq << 32;
@@ -330,7 +330,7 @@ __global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* _
     }
   }
   float v[kChunks][8];
-  if (kMode == 2) {
+  if (kMode == kTpInDataTwoHop) {
     const int owner = row % tp.size;
     const uint64_t tag = (uint64_t)seq << 32;
     // finished rows live behind the 2 x size gathering slots: [2 slots][rows x hidden]
@@ -401,7 +401,7 @@ __global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* _
         add8_bf16(make_uint4((uint32_t)a0, (uint32_t)a1, (uint32_t)a2, (uint32_t)a3), v[c]);
       }
     }
-  } else if (kMode == 1) {
+  } else if (kMode == kTpInDataDirect) {
     // ---- the same row from every peer: each thread polls the words it will sum (its own row is still in registers)
     const long long t0 = clock64();
 #pragma unroll
@@ -410,12 +410,12 @@ __global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* _
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[c][i] = 0.f;
       if (ch >= nchunk) continue;
-      uint4 pr[kTpFlagInDataRanks];
+      uint4 pr[kTpDirectRanks];
       bool all = false;
       while (!all) {
         all = true;
 #pragma unroll
-        for (int r = 0; r < kTpFlagInDataRanks; ++r)
+        for (int r = 0; r < kTpDirectRanks; ++r)
           if (r < tp.size && r != tp.rank) {
             const uint64_t* src = reinterpret_cast<const uint64_t*>(tp.xbuf[tp.rank]) +
                                   ((slot_off + (size_t)r * tp.slot_elems + base + ch * 8) >> 1);
@@ -433,7 +433,7 @@ __global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* _
         }
       }
 #pragma unroll
-      for (int r = 0; r < kTpFlagInDataRanks; ++r)   // rank order, on every rank alike
+      for (int r = 0; r < kTpDirectRanks; ++r)   // rank order, on every rank alike
         if (r < tp.size) add8_bf16(r == tp.rank ? own[c] : pr[r], v[c]);
     }
   } else {
@@ -473,7 +473,7 @@ __global__ void __launch_bounds__(512) exchange_norm_kernel(int kind, const T* _
       continue;
     }
     float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (kMode != 0) {
+    if (kMode != kTpFlagArray) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) { sum[i] = v[c][i]; v[c][i] = 0.f; }
       if (h) load8(h + base + ch * 8, v[c]);
@@ -951,19 +951,19 @@ int exchange_norm(rb_ctx* ctx, const TpPeers& tp, int parity, int kind, const vo
                          acc_stride, (const T*)acc_bias, (const T*)part, (const T*)w, (const T*)b, eps, (int)hidden, (T*)out,
                          (T*)sum_out, tp, parity, ctx->status_dev, ctx->wait_budget_cycles);
   };
-  if (tp.flag_in_data == 1) {
-    RB_REQUIRE(tp.size <= kTpFlagInDataRanks, "exchange_norm: the direct flag-in-data form takes groups of up to %d", kTpFlagInDataRanks);
-    if (chunks == 1) RB_CUDA(go(exchange_norm_kernel<T, 1, 1>));
-    else if (chunks == 2) RB_CUDA(go(exchange_norm_kernel<T, 2, 1>));
-    else RB_CUDA(go(exchange_norm_kernel<T, 4, 1>));
-  } else if (tp.flag_in_data == 2) {
-    if (chunks == 1) RB_CUDA(go(exchange_norm_kernel<T, 1, 2>));
-    else if (chunks == 2) RB_CUDA(go(exchange_norm_kernel<T, 2, 2>));
-    else RB_CUDA(go(exchange_norm_kernel<T, 4, 2>));
+  if (tp.form == kTpInDataDirect) {
+    RB_REQUIRE(tp.size <= kTpDirectRanks, "exchange_norm: the direct flag-in-data form takes groups of up to %d", kTpDirectRanks);
+    if (chunks == 1) RB_CUDA(go(exchange_norm_kernel<T, 1, kTpInDataDirect>));
+    else if (chunks == 2) RB_CUDA(go(exchange_norm_kernel<T, 2, kTpInDataDirect>));
+    else RB_CUDA(go(exchange_norm_kernel<T, 4, kTpInDataDirect>));
+  } else if (tp.form == kTpInDataTwoHop) {
+    if (chunks == 1) RB_CUDA(go(exchange_norm_kernel<T, 1, kTpInDataTwoHop>));
+    else if (chunks == 2) RB_CUDA(go(exchange_norm_kernel<T, 2, kTpInDataTwoHop>));
+    else RB_CUDA(go(exchange_norm_kernel<T, 4, kTpInDataTwoHop>));
   } else {
-    if (chunks == 1) RB_CUDA(go(exchange_norm_kernel<T, 1, 0>));
-    else if (chunks == 2) RB_CUDA(go(exchange_norm_kernel<T, 2, 0>));
-    else RB_CUDA(go(exchange_norm_kernel<T, 4, 0>));
+    if (chunks == 1) RB_CUDA(go(exchange_norm_kernel<T, 1, kTpFlagArray>));
+    else if (chunks == 2) RB_CUDA(go(exchange_norm_kernel<T, 2, kTpFlagArray>));
+    else RB_CUDA(go(exchange_norm_kernel<T, 4, kTpFlagArray>));
   }
   ctx->launches++;
   return RB_OK;

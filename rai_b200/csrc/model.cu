@@ -501,16 +501,16 @@ extern "C" int32_t rb_model_tp_init(rb_model* m, const void* id, int32_t id_byte
   const size_t slot_elems = (size_t)kTpMaxRows * m->cfg.hidden_size;
   // How the exchange signals arrival (see exchange_norm_kernel): 0 = a flag array beside the data; 1 = the flag inside
   // every 8-byte word, sent straight to every peer (a group of two); 2 = the same words over two hops through the
-  // row's owner (wider groups).  RAI_B200_TP_FLAG_IN_DATA=0/1/2 overrides (the same on every rank).
-  int mode = tp <= kTpFlagInDataRanks ? 1 : tp <= kTpTwoHopRanks ? 2 : 0;
-  if (const char* fd = getenv("RAI_B200_TP_FLAG_IN_DATA")) {
+  // row's owner (wider groups).  RAI_B200_TP_EXCHANGE_FORM=0/1/2 overrides (the same on every rank).
+  int mode = tp <= kTpDirectRanks ? kTpInDataDirect : tp <= kTpTwoHopRanks ? kTpInDataTwoHop : kTpFlagArray;
+  if (const char* fd = getenv("RAI_B200_TP_EXCHANGE_FORM")) {
     const int want = atoi(fd);
-    if (want == 0 || want == 2 || (want == 1 && tp <= kTpFlagInDataRanks)) mode = want;
+    if (want == kTpFlagArray || want == kTpInDataTwoHop || (want == kTpInDataDirect && tp <= kTpDirectRanks)) mode = want;
   }
   // flags, then [2 slots][tp sources][rows x hidden] bf16 (4 bytes per element instead of 2 with the flag in the data;
   // the two-hop form adds [2 slots][rows x hidden] for the finished rows)
-  const size_t bytes = kTpFlagBytes + (mode == 0 ? 2 * (size_t)tp * slot_elems * 2
-                                                  : (2 * (size_t)tp + (mode == 2 ? 2 : 0)) * slot_elems * 4);
+  const size_t bytes = kTpFlagBytes + (mode == kTpFlagArray ? 2 * (size_t)tp * slot_elems * 2
+                                                  : (2 * (size_t)tp + (mode == kTpInDataTwoHop ? 2 : 0)) * slot_elems * 4);
   RB_TRY(rb_malloc(ctx, bytes, &m->xchg_base));
   m->owned.push_back(m->xchg_base);
   RB_CUDA(cudaMemsetAsync(m->xchg_base, 0, bytes, ctx->stream));
@@ -565,7 +565,7 @@ extern "C" int32_t rb_model_tp_init(rb_model* m, const void* id, int32_t id_byte
   RB_CUDA(cudaMemsetAsync(local, 0, 256, ctx->stream));
   p.seq = (uint32_t*)local;
   p.rank = rank; p.size = tp; p.slot_elems = (int64_t)slot_elems;
-  p.flag_in_data = mode;
+  p.form = mode;
   // (the vote above was also the meeting point: no rank publishes before every rank has zeroed its region and
   // opened its peers)
   RB_CUDA(cudaStreamSynchronize(ctx->stream));
@@ -781,7 +781,7 @@ extern "C" int32_t rb_model_create(rb_ctx* ctx, const rb_model_config* cfg, rb_m
       p.flags[0] = (uint32_t*)m->xchg_base;
       p.seq = (uint32_t*)((char*)m->xchg_base + kTpFlagBytes);
       p.xbuf[0] = (const char*)m->xchg_base + kTpFlagBytes + 512;
-      p.rank = 0; p.size = 1; p.slot_elems = (int64_t)slot_elems; p.flag_in_data = 0;
+      p.rank = 0; p.size = 1; p.slot_elems = (int64_t)slot_elems; p.form = kTpFlagArray;
       m->peer_base[0] = m->xchg_base;
       m->use_exchange = true;
     }

@@ -94,7 +94,7 @@ extern "C" int32_t rb_selftest_wait_gives_up(rb_ctx* ctx, int32_t which, int64_t
   tp.flags[0] = tp.flags[1] = flags;
   tp.seq = (uint32_t*)((char*)region.p + kTpFlagBytes);
   tp.xbuf[0] = tp.xbuf[1] = (const char*)region.p + kTpFlagBytes + 512;
-  tp.rank = 0; tp.size = 2; tp.slot_elems = (int64_t)slot_elems; tp.flag_in_data = two_hop ? 2 : in_data ? 1 : 0;
+  tp.rank = 0; tp.size = 2; tp.slot_elems = (int64_t)slot_elems; tp.form = two_hop ? kTpInDataTwoHop : in_data ? kTpInDataDirect : kTpFlagArray;
   RB_CUDA(cudaStreamSynchronize(ctx->stream));  // the host buffers above are read by the copies
   const long long keep = ctx->wait_budget_cycles;
   ctx->wait_budget_cycles = budget;
