@@ -435,6 +435,9 @@ def run_ours(args):
     clocks = sampler.summary(t_begin, t_end) if rank == 0 else None
     decode_tok_s = B * K / (decode_ms / 1e3)
     graph_active = bool(_lib.lib().rb_model_decode_graph_active(model._m))
+    if not graph_active and os.environ.get("RAI_B200_GRAPH") != "0":
+        # a capture that failed would fall back to plain launches for the model's life: not a number to report quietly
+        raise SystemExit("bench: the decode step did not run as a captured graph (RAI_B200_VERBOSE=1 says why)")
 
     # ---- per-kernel-class timing of the same steps (event pair around every launch; separate pass)
     classes = ["gemm", "attention", "norm", "rope_kv", "embed", "argmax", "other"]
