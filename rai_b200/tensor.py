@@ -133,6 +133,13 @@ class Tensor:
     def t(self) -> "Tensor":
         return self.transpose(-1, -2)
 
+    def permute(self, dims) -> "Tensor":   # ops/permute.rs:51-60: output dimension i is input dimension dims[i]
+        r = len(self.shape)
+        dims = [_resolve_dim(int(d), r) for d in dims]
+        if sorted(dims) != list(range(r)):
+            raise _lib.RaiB200Error(-2, f"permute{tuple(dims)} is not a permutation of the {r} dimensions of {self.shape}")
+        return self._view([self.shape[d] for d in dims], [self.strides[d] for d in dims], self.offset)
+
     def narrow(self, dim: int, start: int, length: int) -> "Tensor":   # ops/narrow.rs:82-90
         d = _resolve_dim(dim, len(self.shape))
         if start < 0 or start + length > self.shape[d]:

@@ -75,6 +75,10 @@ def test_tensor_views_and_shape_algebra(cuda):
     x = np.arange(2 * 3 * 4, dtype=np.float32).reshape(2, 3, 4)
     t = T(x, cuda)
     assert np.array_equal(t.transpose(0, 2).as_vec(), x.transpose(2, 1, 0))
+    assert np.array_equal(t.permute([2, 0, 1]).as_vec(), x.transpose(2, 0, 1))          # ops/permute.rs
+    assert np.array_equal(t.permute([-1, 0, 1]).narrow(0, 1, 2).as_vec(), x.transpose(2, 0, 1)[1:3])
+    with pytest.raises(_lib.RaiB200Error):
+        t.permute([0, 0, 1])
     assert np.array_equal(t.narrow(-1, 1, 2).as_vec(), x[..., 1:3])
     assert np.array_equal(t.narrow(1, 2, 1).squeeze(1).as_vec(), x[:, 2])
     assert np.array_equal(t.unsqueeze(0).broadcast_to([5, 2, 3, 4]).as_vec(), np.broadcast_to(x, (5, 2, 3, 4)))
