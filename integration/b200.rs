@@ -201,6 +201,15 @@ const UN_COS: i32 = 8;
 const UN_POWF: i32 = 9;
 const UN_LOG: i32 = 14;
 const UN_ABS: i32 = 15;
+const UN_SIGN: i32 = 19;
+const UN_LOG2: i32 = 20;
+const UN_LOG10: i32 = 21;
+const CMP_EQ: i32 = 0;
+const CMP_NE: i32 = 1;
+const CMP_GT: i32 = 2;
+const CMP_GE: i32 = 3;
+const CMP_LT: i32 = 4;
+const CMP_LE: i32 = 5;
 const BIN_ADD: i32 = 0;
 const BIN_SUB: i32 = 1;
 const BIN_MUL: i32 = 2;
@@ -552,6 +561,9 @@ unary_rule!(ops::Sin, UN_SIN);
 unary_rule!(ops::Cos, UN_COS);
 unary_rule!(ops::Log, UN_LOG);
 unary_rule!(ops::Abs, UN_ABS);
+unary_rule!(ops::Sign, UN_SIGN);
+unary_rule!(ops::Log2, UN_LOG2);
+unary_rule!(ops::Log10, UN_LOG10);
 
 impl<T: Type> Eval<Cuda, ops::Powf<T>> for B200Backend
 where
@@ -593,6 +605,33 @@ binary_rule!(ops::Mul, BIN_MUL);
 binary_rule!(ops::Div, BIN_DIV);
 binary_rule!(ops::Maximum, BIN_MAXIMUM);
 binary_rule!(ops::Minimum, BIN_MINIMUM);
+
+// Comparisons (candle.rs:628-752): U8 results, operands as the binary rules take them.
+macro_rules! compare_rule {
+    ($op:ty, $tag:expr) => {
+        impl Eval<Cuda, $op> for B200Backend {
+            fn eval(&self, _: &Cuda, _: &$op, inputs: &[Tensor], output: &Tensor) {
+                let (a, b) = (data(&inputs[0]), data(&inputs[1]));
+                assert!(a.shape.len() <= 4, "rb_compare takes up to 4 dimensions; flatten leading ones first");
+                let out = B200Tensor::alloc(a.ctx(), output.shape(), output.dtype());
+                let shape: Vec<i64> = a.shape.iter().map(|&d| d as i64).collect();
+                let sa: Vec<i64> = a.strides.iter().map(|&d| d as i64).collect();
+                let sb: Vec<i64> = b.strides.iter().map(|&d| d as i64).collect();
+                check(unsafe {
+                    rb_compare(a.ctx(), $tag, a.ptr(), sa.as_ptr(), b.ptr(), sb.as_ptr(), out.ptr() as *mut u8,
+                               shape.len() as i32, shape.as_ptr(), tag(a.dtype.as_ref()))
+                });
+                output.set_data(out);
+            }
+        }
+    };
+}
+compare_rule!(ops::Equal, CMP_EQ);
+compare_rule!(ops::NotEqual, CMP_NE);
+compare_rule!(ops::Greater, CMP_GT);
+compare_rule!(ops::GreaterEqual, CMP_GE);
+compare_rule!(ops::Less, CMP_LT);
+compare_rule!(ops::LessEqual, CMP_LE);
 
 impl<T: Type> Eval<Cuda, ops::ToDType<T>> for B200Backend {
     fn eval(&self, _: &Cuda, _: &ops::ToDType<T>, inputs: &[Tensor], output: &Tensor) {
@@ -663,6 +702,20 @@ impl Eval<Cuda, ops::Softmax> for B200Backend {
     }
 }
 
+// LogSoftmax (candle.rs:805-826), the same row layout as Softmax.
+impl Eval<Cuda, ops::LogSoftmax> for B200Backend {
+    fn eval(&self, _: &Cuda, op: &ops::LogSoftmax, inputs: &[Tensor], output: &Tensor) {
+        let x = data(&inputs[0]);
+        let last = x.shape.len() - 1;
+        let moved = if op.dim == last { x.dense() } else { transpose_view(&x, op.dim, last).dense() };
+        let cols = *moved.shape.last().unwrap();
+        let rows = moved.numel() / cols;
+        let y = B200Tensor::alloc(x.ctx(), &moved.shape, x.dtype.as_ref());
+        check(unsafe { rb_log_softmax_rows(x.ctx(), moved.ptr(), y.ptr(), rows as i64, cols as i64, tag(x.dtype.as_ref())) });
+        output.set_data(if op.dim == last { y } else { transpose_view(&y, op.dim, last).dense() });
+    }
+}
+
 // ReduceSum / ReduceMax / ReduceMin over any set of dims (ops/reduce_sum.rs:63-76, candle.rs:475-523): the reduced
 // dims are permuted to the end and flattened, then one row reduction.
 fn reduce(x: &B200Tensor, dims: &[usize], keep_dim: bool, kind: i32, out_shape: &[usize]) -> B200Tensor {
@@ -709,6 +762,22 @@ impl Eval<Cuda, ops::ArgMax> for B200Backend {
     }
 }
 
+// ArgMin (candle.rs:933-945): as ArgMax.
+impl Eval<Cuda, ops::ArgMin> for B200Backend {
+    fn eval(&self, _: &Cuda, op: &ops::ArgMin, inputs: &[Tensor], output: &Tensor) {
+        let x = data(&inputs[0]);
+        let last = x.shape.len() - 1;
+        let moved = if op.dim == last { x.dense() } else { transpose_view(&x, op.dim, last).dense() };
+        let cols = *moved.shape.last().unwrap();
+        let rows = moved.numel() / cols;
+        let out = B200Tensor::alloc(x.ctx(), output.shape(), output.dtype());
+        check(unsafe {
+            rb_argmin_rows(x.ctx(), moved.ptr(), tag(x.dtype.as_ref()), rows as i64, cols as i64, out.ptr() as *mut u32)
+        });
+        output.set_data(out);
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ indexing
 // IndexSelect (candle.rs:867-878): x viewed as [outer, dim, inner]; bit-exact row copies.
 impl Eval<Cuda, ops::IndexSelect> for B200Backend {
@@ -743,6 +812,143 @@ impl Eval<Cuda, ops::Gather> for B200Backend {
             rb_gather_last(x.ctx(), xm.ptr(), rows as i64, cols as i64, im.ptr() as *const u32, k as i64, y.ptr(), x.es() as i32)
         });
         output.set_data(if op.dim == last { y } else { transpose_view(&y, op.dim, last).dense() });
+    }
+}
+
+// ScatterAdd / IndexAdd (candle.rs:851-865, 991-1004): inputs are [x, source, index]; x viewed as [outer, dim, inner].
+// ScatterAdd's index has the source's shape, IndexAdd's is one-dimensional along `dim`.
+fn scatter(x: &B200Tensor, src: &B200Tensor, idx: &B200Tensor, dim: usize, index_is_1d: bool, output: &Tensor) {
+    let (x, src, idx) = (x.dense(), src.dense(), idx.dense());
+    let outer: usize = x.shape[..dim].iter().product();
+    let inner: usize = x.shape[dim + 1..].iter().product();
+    let out = B200Tensor::alloc(x.ctx(), output.shape(), output.dtype());
+    check(unsafe {
+        rb_scatter_add(x.ctx(), x.ptr(), src.ptr(), idx.ptr() as *const u32, out.ptr(), outer as i64, x.shape[dim] as i64,
+                       src.shape[dim] as i64, inner as i64, index_is_1d as i32, tag(x.dtype.as_ref()))
+    });
+    output.set_data(out);
+}
+impl Eval<Cuda, ops::ScatterAdd> for B200Backend {
+    fn eval(&self, _: &Cuda, op: &ops::ScatterAdd, inputs: &[Tensor], output: &Tensor) {
+        scatter(&data(&inputs[0]), &data(&inputs[1]), &data(&inputs[2]), op.dim, false, output);
+    }
+}
+impl Eval<Cuda, ops::IndexAdd> for B200Backend {
+    fn eval(&self, _: &Cuda, op: &ops::IndexAdd, inputs: &[Tensor], output: &Tensor) {
+        scatter(&data(&inputs[0]), &data(&inputs[1]), &data(&inputs[2]), op.dim, true, output);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ convolutions, pools
+// NCHW activations, [out, in, kh, kw] weights ([in, out, kh, kw] transposed), as candle.rs:1006-1150 passes them on.
+// The 1-D forms run as the 2-D ones over a height of one.
+fn i32x4(shape: &[usize]) -> [i32; 4] {
+    [shape[0] as i32, shape[1] as i32, shape[2] as i32, shape[3] as i32]
+}
+fn with_unit_height(x: &B200Tensor) -> B200Tensor {
+    let d = x.dense();
+    let shape = vec![d.shape[0], d.shape[1], 1, d.shape[2]];
+    let strides = dense_strides(&shape);
+    d.view(d.offset, shape, strides)
+}
+fn conv2d(x: &B200Tensor, w: &B200Tensor, padding: [i32; 2], stride: [i32; 2], dilation: [i32; 2], output: &Tensor) {
+    let (x, w) = (x.dense(), w.dense());
+    let mut oshape = [0i32; 4];
+    let out = B200Tensor::alloc(x.ctx(), output.shape(), output.dtype());
+    check(unsafe {
+        rb_conv2d(x.ctx(), x.ptr(), i32x4(&x.shape).as_ptr(), w.ptr(), i32x4(&w.shape).as_ptr(), padding.as_ptr(),
+                  stride.as_ptr(), dilation.as_ptr(), out.ptr(), oshape.as_mut_ptr(), tag(x.dtype.as_ref()))
+    });
+    output.set_data(out);   // the node's own shape ([N, C, L] for the 1-D form) over the same dense bytes
+}
+impl Eval<Cuda, ops::Conv2d> for B200Backend {
+    fn eval(&self, _: &Cuda, op: &ops::Conv2d, inputs: &[Tensor], output: &Tensor) {
+        let p = |a: [usize; 2]| [a[0] as i32, a[1] as i32];
+        conv2d(&data(&inputs[0]), &data(&inputs[1]), p(op.padding), p(op.stride), p(op.dilation), output);
+    }
+}
+impl Eval<Cuda, ops::Conv1d> for B200Backend {
+    fn eval(&self, _: &Cuda, op: &ops::Conv1d, inputs: &[Tensor], output: &Tensor) {
+        conv2d(&with_unit_height(&data(&inputs[0])), &with_unit_height(&data(&inputs[1])), [0, op.padding as i32],
+               [1, op.stride as i32], [1, op.dilation as i32], output);
+    }
+}
+fn conv_transpose2d(x: &B200Tensor, w: &B200Tensor, padding: [i32; 2], out_padding: [i32; 2], stride: [i32; 2],
+                    dilation: [i32; 2], output: &Tensor) {
+    let (x, w) = (x.dense(), w.dense());
+    let mut oshape = [0i32; 4];
+    let out = B200Tensor::alloc(x.ctx(), output.shape(), output.dtype());
+    check(unsafe {
+        rb_conv_transpose2d(x.ctx(), x.ptr(), i32x4(&x.shape).as_ptr(), w.ptr(), i32x4(&w.shape).as_ptr(), padding.as_ptr(),
+                            out_padding.as_ptr(), stride.as_ptr(), dilation.as_ptr(), out.ptr(), oshape.as_mut_ptr(),
+                            tag(x.dtype.as_ref()))
+    });
+    output.set_data(out);
+}
+impl Eval<Cuda, ops::ConvTranspose2d> for B200Backend {
+    fn eval(&self, _: &Cuda, op: &ops::ConvTranspose2d, inputs: &[Tensor], output: &Tensor) {
+        let p = |a: [usize; 2]| [a[0] as i32, a[1] as i32];
+        conv_transpose2d(&data(&inputs[0]), &data(&inputs[1]), p(op.padding), p(op.out_padding), p(op.stride),
+                         p(op.dilation), output);
+    }
+}
+impl Eval<Cuda, ops::ConvTranspose1d> for B200Backend {
+    fn eval(&self, _: &Cuda, op: &ops::ConvTranspose1d, inputs: &[Tensor], output: &Tensor) {
+        conv_transpose2d(&with_unit_height(&data(&inputs[0])), &with_unit_height(&data(&inputs[1])), [0, op.padding as i32],
+                         [0, op.output_padding as i32], [1, op.stride as i32], [1, op.dilation as i32], output);
+    }
+}
+fn pool2d(x: &B200Tensor, is_max: bool, kernel: [i32; 2], stride: [i32; 2], padding: [i32; 2], dilation: [i32; 2],
+          output: &Tensor) {
+    let x = x.dense();
+    let mut oshape = [0i32; 4];
+    let out = B200Tensor::alloc(x.ctx(), output.shape(), output.dtype());
+    check(unsafe {
+        rb_pool2d(x.ctx(), is_max as i32, x.ptr(), i32x4(&x.shape).as_ptr(), kernel.as_ptr(), stride.as_ptr(),
+                  padding.as_ptr(), dilation.as_ptr(), out.ptr(), oshape.as_mut_ptr(), tag(x.dtype.as_ref()))
+    });
+    output.set_data(out);
+}
+impl Eval<Cuda, ops::MaxPool2d> for B200Backend {
+    fn eval(&self, _: &Cuda, op: &ops::MaxPool2d, inputs: &[Tensor], output: &Tensor) {
+        let p = |a: (usize, usize)| [a.0 as i32, a.1 as i32];
+        pool2d(&data(&inputs[0]), true, p(op.kernel_size), p(op.stride), p(op.padding), p(op.dilation), output);
+    }
+}
+impl Eval<Cuda, ops::AvgPool2d> for B200Backend {
+    fn eval(&self, _: &Cuda, op: &ops::AvgPool2d, inputs: &[Tensor], output: &Tensor) {
+        let p = |a: (usize, usize)| [a.0 as i32, a.1 as i32];
+        pool2d(&data(&inputs[0]), false, p(op.kernel_size), p(op.stride), p(op.padding), [1, 1], output);
+    }
+}
+impl Eval<Cuda, ops::MaxPool1d> for B200Backend {
+    fn eval(&self, _: &Cuda, op: &ops::MaxPool1d, inputs: &[Tensor], output: &Tensor) {
+        pool2d(&with_unit_height(&data(&inputs[0])), true, [1, op.kernel_size as i32], [1, op.stride as i32],
+               [0, op.padding as i32], [1, op.dilation as i32], output);
+    }
+}
+impl Eval<Cuda, ops::AvgPool1d> for B200Backend {
+    fn eval(&self, _: &Cuda, op: &ops::AvgPool1d, inputs: &[Tensor], output: &Tensor) {
+        pool2d(&with_unit_height(&data(&inputs[0])), false, [1, op.kernel_size as i32], [1, op.stride as i32],
+               [0, op.padding as i32], [1, 1], output);
+    }
+}
+fn upsample_nearest2d(x: &B200Tensor, h: usize, w: usize, output: &Tensor) {
+    let x = x.dense();
+    let out = B200Tensor::alloc(x.ctx(), output.shape(), output.dtype());
+    check(unsafe {
+        rb_upsample_nearest2d(x.ctx(), x.ptr(), i32x4(&x.shape).as_ptr(), h as i32, w as i32, out.ptr(), tag(x.dtype.as_ref()))
+    });
+    output.set_data(out);
+}
+impl Eval<Cuda, ops::UpsampleNearest2d> for B200Backend {
+    fn eval(&self, _: &Cuda, op: &ops::UpsampleNearest2d, inputs: &[Tensor], output: &Tensor) {
+        upsample_nearest2d(&data(&inputs[0]), op.size.0, op.size.1, output);
+    }
+}
+impl Eval<Cuda, ops::UpsampleNearest1d> for B200Backend {
+    fn eval(&self, _: &Cuda, op: &ops::UpsampleNearest1d, inputs: &[Tensor], output: &Tensor) {
+        upsample_nearest2d(&with_unit_height(&data(&inputs[0])), 1, op.size, output);
     }
 }
 
@@ -820,9 +1026,8 @@ impl Eval<Cuda, ops::Concatenate> for B200Backend {
 
 // ------------------------------------------------------------------------------------------------ registration
 /// Installs the rules above for `Cuda`, key by key like `register_backend!` (dispatch.rs:41-157).  Ops of that list
-/// with no rule here stay unregistered for `Cuda` and evaluate to `Error::Unimplemented` (eval.rs:40-43): Random,
-/// Normal, the comparisons, Sign, Log2, Log10, LogSoftmax, ScatterAdd, IndexAdd, ArgMin, the convolutions, pools
-/// and upsampling — none of which the four decoders reach.
+/// with no rule here stay unregistered for `Cuda` and evaluate to `Error::Unimplemented` (eval.rs:40-43): Random and
+/// Normal, which nothing on the decoders' path reaches.
 pub fn register_all() {
     let b = B200Backend;
     macro_rules! reg {
@@ -844,7 +1049,11 @@ pub fn register_all() {
         ops::Softmax, ops::ToDevice<Cpu>, ops::ToDevice<Cuda>,
         ops::Gather, ops::IndexSelect, ops::Narrow, ops::Where,
         ops::Transpose, ops::Reshape, ops::Permute, ops::Broadcast, ops::ToContiguous,
-        ops::ReduceSum, ops::ReduceMax, ops::ReduceMin, ops::ArgMax,
+        ops::ReduceSum, ops::ReduceMax, ops::ReduceMin, ops::ArgMax, ops::ArgMin,
+        ops::Equal, ops::NotEqual, ops::Greater, ops::GreaterEqual, ops::Less, ops::LessEqual,
+        ops::Sign, ops::Log2, ops::Log10, ops::LogSoftmax, ops::ScatterAdd, ops::IndexAdd,
+        ops::Conv1d, ops::Conv2d, ops::ConvTranspose1d, ops::ConvTranspose2d,
+        ops::MaxPool1d, ops::MaxPool2d, ops::AvgPool1d, ops::AvgPool2d, ops::UpsampleNearest1d, ops::UpsampleNearest2d,
     );
     // the upload direction is keyed by the SOURCE device (dispatch.rs:207-212 looks rules up by the node's device)
     dispatch::register::<Cpu, ops::ToDevice<Cuda>, B200Backend>(b);
